@@ -138,7 +138,12 @@ class CacheManager:
                 if isinstance(item, PagedKVNeed):
                     if item.window is not None and item.window <= 0:
                         raise ValueError(f"cache slot {slot}: window {item.window} must be positive")
-                    key = (item.n_kv_heads, item.head_dim, item.window, item.value_dim, item.values_are_keys)
+                    if item.n_kv_heads % item.value_heads or (item.values_are_keys and (
+                            item.value_heads != item.n_kv_heads or item.value_dim > item.head_dim)):
+                        raise ValueError(f"cache slot {slot}: {item.value_heads} value heads of {item.value_dim} under "
+                                         f"{item.n_kv_heads} key heads of {item.head_dim}")
+                    key = (item.n_kv_heads, item.head_dim, item.window, item.value_dim, item.values_are_keys,
+                           item.value_heads)
                     g = by_key.get(key)
                     if g is None:
                         g = CacheGroup(len(self.groups), item, [], page_size, IdPool(num_pages, "page"))
@@ -160,9 +165,16 @@ class CacheManager:
         if allocate:
             for g in self.groups:
                 L, G, hd, vd = len(g.slots), g.need.n_kv_heads, g.need.head_dim, g.need.value_dim
+                Gv = g.need.value_heads
                 if g.need.values_are_keys:
                     g.storage = torch.zeros((L, num_pages, G, page_size, hd), dtype=dtype, device=self.device)
                     g.k_store = g.v_store = g.storage
+                elif Gv != G:
+                    # fewer value heads than key heads: two stores of their own shapes in one allocation
+                    rows = L * num_pages * page_size
+                    g.storage = torch.zeros(rows * (G * hd + Gv * vd), dtype=dtype, device=self.device)
+                    g.k_store = g.storage[:rows * G * hd].view(L, num_pages, G, page_size, hd)
+                    g.v_store = g.storage[rows * G * hd:].view(L, num_pages, Gv, page_size, vd)
                 elif vd == hd:
                     g.storage = torch.zeros((L, 2, num_pages, G, page_size, hd), dtype=dtype, device=self.device)
                     g.k_store, g.v_store = g.storage[:, 0], g.storage[:, 1]
@@ -180,7 +192,7 @@ class CacheManager:
         """Device bytes that one more page in EVERY group's pool costs: keys and values of
         all layers of all groups (the pools have the same number of pages)."""
         esize = torch.empty((), dtype=self.dtype).element_size()
-        return sum(len(g.slots) * g.need.n_kv_heads * self.page_size * g.need.stored_dim * esize
+        return sum(len(g.slots) * self.page_size * g.need.stored_per_token * esize
                    for g in self.groups)
 
     @classmethod
@@ -202,7 +214,7 @@ class CacheManager:
         """Cache bytes that one more token of context costs in the groups that keep
         every key."""
         esize = torch.empty((), dtype=self.dtype).element_size()
-        return sum(len(g.slots) * g.need.n_kv_heads * g.need.stored_dim * esize
+        return sum(len(g.slots) * g.need.stored_per_token * esize
                    for g in self.groups if g.window is None)
 
     def pages_ever_needed(self, total_tokens: int) -> List[int]:

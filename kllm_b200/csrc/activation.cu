@@ -9,6 +9,23 @@ KLLM_EXPORT_LAST_ERROR(activation)
 
 namespace {
 
+// out = a * sigmoid(gate): a gate on a mixer's output, the logits float32 (they come unrounded from
+// their product), a and out in the model's element type.
+template <typename T>
+__global__ void sigmoid_gate_kernel(T* __restrict__ out, int64_t out_stride, const T* __restrict__ a, int64_t a_stride,
+                                    const float* __restrict__ gate, int64_t gate_stride, int n, int f) {
+    griddep_wait();
+    griddep_launch();
+    const int64_t total = (int64_t)n * f;
+    for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+         idx += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t r = idx / f;
+        const int c = (int)(idx - r * f);
+        const float g = gate[r * gate_stride + c];
+        out[r * out_stride + c] = from_f32<T>(to_f32(a[r * a_stride + c]) / (1.f + expf(-g)));
+    }
+}
+
 template <typename T, typename I>
 __global__ void silu_mul_kernel(T* __restrict__ out, int64_t out_stride,
                                 const I* __restrict__ gate, int64_t gate_stride,
@@ -159,5 +176,24 @@ extern "C" int kllm_silu_mul(void* out, int64_t out_stride, const void* gate, in
             (bf16*)out, out_stride, (const float*)gate, gate_stride, (const float*)up, up_stride, n, f);
     else
         KLLM_FAIL("silu_mul: element types %d (out) and %d (in) are not supported together", dtype, in_dtype);
+    KLLM_LAUNCH_STATUS();
+}
+
+// out [n][f] = a [n][f] * sigmoid(gate [n][f]); a and out of element type `dtype`, gate float32; row
+// strides in elements.
+extern "C" int kllm_sigmoid_gate(void* out, int64_t out_stride, const void* a, int64_t a_stride, const float* gate,
+                                 int64_t gate_stride, int n, int f, int dtype, void* stream) {
+    if (n <= 0 || f <= 0) return 0;
+    cudaStream_t s = (cudaStream_t)stream;
+    int64_t blocks = ((int64_t)n * f + 255) / 256;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    if (dtype == KLLM_F32)
+        kllm_launch((sigmoid_gate_kernel<float>), dim3((unsigned)blocks), dim3(256), 0, s, (float*)out, out_stride,
+                    (const float*)a, a_stride, gate, gate_stride, n, f);
+    else if (dtype == KLLM_BF16)
+        kllm_launch((sigmoid_gate_kernel<bf16>), dim3((unsigned)blocks), dim3(256), 0, s, (bf16*)out, out_stride,
+                    (const bf16*)a, a_stride, gate, gate_stride, n, f);
+    else
+        KLLM_FAIL("sigmoid gate: unknown element type %d", dtype);
     KLLM_LAUNCH_STATUS();
 }

@@ -65,7 +65,8 @@ attn_simt_kernel(T* __restrict__ out, float* __restrict__ part_o, float* __restr
                  const T* __restrict__ vcache, const int* __restrict__ q_start, const int* __restrict__ start_pos,
                  const int* __restrict__ block_table, int max_blocks, int n_requests, int n_heads, int n_kv, int hd,
                  int vd, int page_size, int window, float scale, int qt, int chunk, int max_splits,
-                 const float* __restrict__ slopes, const float* __restrict__ sinks) {
+                 const float* __restrict__ slopes, const float* __restrict__ sinks, int segment, int v_heads,
+                 int v_row, int out_f32) {
     extern __shared__ __align__(16) float sm[];
     const int ld = hd + 4, ldv = vd + 4;
     float* Qs = sm;
@@ -102,7 +103,8 @@ attn_simt_kernel(T* __restrict__ out, float* __restrict__ part_o, float* __restr
     const int R = nq * gs;
     const int tok0 = q_start[s] + q0;
     const int p0 = start_pos[s] + q0;                       // position of the tile's first token
-    const int lo_all = (window > 0 && p0 + 1 > window) ? p0 + 1 - window : 0;
+    int lo_all = (window > 0 && p0 + 1 > window) ? p0 + 1 - window : 0;
+    if (segment > 0) lo_all = max(lo_all, p0 - p0 % segment);      // the first token's segment starts no later than the others'
     const int hi_all = p0 + nq;
     int lo = lo_all, hi = hi_all;
     if (chunk > 0) {
@@ -138,6 +140,7 @@ attn_simt_kernel(T* __restrict__ out, float* __restrict__ part_o, float* __restr
         pos[i] = r < R ? p0 + r / gs : -1;                  // -1: no key is visible to a row that does not exist
         slope[i] = (slopes && r < R) ? slopes[g * gs + r % gs] : 0.f;
         wlo[i] = window > 0 ? pos[i] + 1 - window : 0;
+        if (segment > 0 && pos[i] >= 0) wlo[i] = max(wlo[i], pos[i] - pos[i] % segment);
 #pragma unroll
         for (int c = 0; c < NC; c++) acc[i][c] = make_float4(0.f, 0.f, 0.f, 0.f);
     }
@@ -150,10 +153,13 @@ attn_simt_kernel(T* __restrict__ out, float* __restrict__ part_o, float* __restr
             // four threads per key: one look-up of the key's page, then independent 16-byte loads
             const int k = tid >> 2, kp = key0 + k;
             const bool ok = kp < hi;
-            int64_t off = 0;
+            int64_t off = 0, offv = 0;
             if (ok) {
                 const int lp = kp / page_size;
                 off = ((int64_t)table[lp] * n_kv + g) * page_size + (kp - lp * page_size);
+                // values may have fewer heads than keys (several key heads on one value head) and rows of
+                // another stride (a row of values that is the head of a longer row)
+                offv = (((int64_t)table[lp] * v_heads + g / (n_kv / v_heads)) * page_size + (kp - lp * page_size)) * v_row;
             }
 #pragma unroll 4
             for (int c = tid & 3; c < hd4; c += 4) {
@@ -164,7 +170,7 @@ attn_simt_kernel(T* __restrict__ out, float* __restrict__ part_o, float* __restr
 #pragma unroll 4
             for (int c = tid & 3; c < vd4; c += 4) {
                 float4 vv = make_float4(0.f, 0.f, 0.f, 0.f);
-                if (ok) vv = load4(vcache + off * vd + 4 * c);
+                if (ok) vv = load4(vcache + offv + 4 * c);
                 *reinterpret_cast<float4*>(Vs + k * ldv + 4 * c) = vv;
             }
         }
@@ -268,9 +274,11 @@ attn_simt_kernel(T* __restrict__ out, float* __restrict__ part_o, float* __restr
 #pragma unroll
             for (int c = 0; c < NC; c++) {
                 const int d = 4 * tx + 64 * c;
-                if (d < vd)
-                    store4(out + row * vd + d, make_float4(acc[i][c].x * inv, acc[i][c].y * inv,
-                                                           acc[i][c].z * inv, acc[i][c].w * inv));
+                if (d < vd) {
+                    const float4 o4 = make_float4(acc[i][c].x * inv, acc[i][c].y * inv, acc[i][c].z * inv, acc[i][c].w * inv);
+                    if (out_f32) store4(reinterpret_cast<float*>(out) + row * vd + d, o4);
+                    else store4(out + row * vd + d, o4);
+                }
             }
         } else {
             float* po = part_o + (row * max_splits + split) * vd;
@@ -506,14 +514,15 @@ template <typename T>
 __global__ void __launch_bounds__(128)
 attn_simt_merge_kernel(T* __restrict__ out, const float* __restrict__ part_o, const float* __restrict__ part_ml,
                        const int* __restrict__ positions, int n_rows, int n_heads, int hd, int window, int chunk,
-                       int max_splits, const float* __restrict__ sinks) {
+                       int max_splits, const float* __restrict__ sinks, int segment, int out_f32) {
     griddep_wait();
     griddep_launch();
     const int lane = threadIdx.x & 31;
     const int64_t row = (int64_t)blockIdx.x * 4 + (threadIdx.x >> 5);
     if (row >= n_rows) return;
     const int p = positions[row / n_heads];
-    const int lo_all = (window > 0 && p + 1 > window) ? p + 1 - window : 0;
+    int lo_all = (window > 0 && p + 1 > window) ? p + 1 - window : 0;
+    if (segment > 0) lo_all = max(lo_all, p - p % segment);
     const int ns = (p + 1 - lo_all + chunk - 1) / chunk;
     // the chunks' maxima first (all loads at once), then their weights, then the sums in chunk order
     const float sink = sinks ? sinks[row % n_heads] : -INFINITY;
@@ -554,7 +563,10 @@ attn_simt_merge_kernel(T* __restrict__ out, const float* __restrict__ part_o, co
 #pragma unroll
     for (int i = 0; i < 8; i++) {
         const int d = lane + 32 * i;
-        if (d < hd) out[row * hd + d] = from_f32<T>(o[i] * inv);
+        if (d < hd) {
+            if (out_f32) reinterpret_cast<float*>(out)[row * hd + d] = o[i] * inv;
+            else out[row * hd + d] = from_f32<T>(o[i] * inv);
+        }
     }
 }
 
@@ -564,7 +576,8 @@ template <typename T, int NC>
 int launch(void* out, float* part_o, float* part_ml, const void* q, int64_t q_stride, const void* kcache,
            const void* vcache, const int* q_start, const int* start_pos, const int* block_table, int max_blocks,
            int n_requests, int max_tiles, int n_heads, int n_kv, int hd, int vd, int page_size, int window, float scale,
-           int qt, int chunk, int max_splits, const float* slopes, const float* sinks, cudaStream_t s) {
+           int qt, int chunk, int max_splits, const float* slopes, const float* sinks, int segment, int v_heads,
+           int v_row, int out_f32, cudaStream_t s) {
     auto kern = attn_simt_kernel<T, NC>;
     static bool raised = false;
     const size_t smem = smem_bytes(hd, vd);
@@ -578,7 +591,8 @@ int launch(void* out, float* part_o, float* part_ml, const void* q, int64_t q_st
     }
     kllm_launch(kern, dim3(max_tiles * n_kv, 1, chunk > 0 ? max_splits : 1), dim3(THREADS), smem, s, (T*)out, part_o,
                 part_ml, (const T*)q, q_stride, (const T*)kcache, (const T*)vcache, q_start, start_pos, block_table,
-                max_blocks, n_requests, n_heads, n_kv, hd, vd, page_size, window, scale, qt, chunk, max_splits, slopes, sinks);
+                max_blocks, n_requests, n_heads, n_kv, hd, vd, page_size, window, scale, qt, chunk, max_splits, slopes, sinks,
+                segment, v_heads, v_row, out_f32);
     KLLM_LAUNCH_STATUS();
 }
 
@@ -596,17 +610,25 @@ int launch(void* out, float* part_o, float* part_ml, const void* q, int64_t q_st
 // slopes: optional float32 [n_heads]; slope[h] * (key position - query position) is added to
 // the scaled scores of head h.  sinks: optional float32 [n_heads]; exp(sinks[h]) is added to the
 // denominator of head h's softmax (unscaled, once: with chunks, kllm_attention_simt_merge adds it).
+// segment > 0: positions are cut into segments of that many, counted from 0, and a query sees only the
+// keys of its own segment (beside the causal rule and the window).  v_heads: heads of the value store
+// (n_kv / v_heads neighbouring key heads read one value head); v_row: elements between two value rows
+// (vd, or more when a value row is the head of a longer row, e.g. of the key row itself).
+// out_f32: `out` is float32 whatever the operands' type.
 extern "C" int kllm_attention_simt(void* out, void* part_o, void* part_ml, const void* q, int64_t q_stride,
                                    const void* kcache, const void* vcache, const int* q_start, const int* start_pos,
                                    const int* block_table, int max_blocks, int n_requests, int max_tiles,
                                    int n_heads, int n_kv, int hd, int vd, int page_size, int window, float scale, int qt,
-                                   int chunk, int max_splits, const float* slopes, const float* sinks, int dtype,
-                                   void* stream) {
+                                   int chunk, int max_splits, const float* slopes, const float* sinks, int segment,
+                                   int v_heads, int v_row, int out_f32, int dtype, void* stream) {
     if (n_requests <= 0 || max_tiles <= 0) return 0;
     if (hd <= 0 || hd > 256 || hd % 4) KLLM_FAIL("attention (simt): head size %d is not a multiple of 4 up to 256", hd);
     if (vd <= 0 || vd > 256 || vd % 4) KLLM_FAIL("attention (simt): value size %d is not a multiple of 4 up to 256", vd);
     if (n_kv <= 0 || n_heads % n_kv) KLLM_FAIL("attention (simt): %d heads over %d kv heads", n_heads, n_kv);
     const int gs = n_heads / n_kv;
+    if (segment < 0 || v_heads <= 0 || n_kv % v_heads || v_row < vd || v_row % 4)
+        KLLM_FAIL("attention (simt): segment %d, %d value heads under %d key heads, value rows of %d at a stride of %d",
+                  segment, v_heads, n_kv, vd, v_row);
     if (qt < 1 || qt * gs > ROWS) KLLM_FAIL("attention (simt): %d tokens x %d heads exceed the %d rows of a tile", qt, gs, ROWS);
     if (page_size <= 0) KLLM_FAIL("attention (simt): page size %d", page_size);
     if (chunk < 0 || (chunk > 0 && (qt != 1 || max_splits < 1 || !part_o || !part_ml || n_kv > 65535 || max_splits > 65535)))
@@ -616,7 +638,8 @@ extern "C" int kllm_attention_simt(void* out, void* part_o, void* part_ml, const
         KLLM_FAIL("attention (simt): operands must be aligned to four elements");
     cudaStream_t s = (cudaStream_t)stream;
     // decoding tokens in float32 at the common head sizes and group widths: the kernel in which every thread works
-    if (chunk > 0 && dtype == KLLM_F32 && (hd == 64 || hd == 128) && vd == hd && n_requests == max_tiles) {
+    if (chunk > 0 && dtype == KLLM_F32 && (hd == 64 || hd == 128) && vd == hd && n_requests == max_tiles && segment == 0 &&
+        v_heads == n_kv && v_row == vd) {
 #define KLLM_SIMT_DEC(HD_, GS_)                                                                                        \
     if (hd == HD_ && gs == GS_)                                                                                       \
         return launch_decode<HD_, GS_>((float*)part_o, (float*)part_ml, q, q_stride, kcache, vcache, q_start, start_pos, \
@@ -629,7 +652,7 @@ extern "C" int kllm_attention_simt(void* out, void* part_o, void* part_ml, const
 #define KLLM_SIMT(T, NC)                                                                                              \
     return launch<T, NC>(out, (float*)part_o, (float*)part_ml, q, q_stride, kcache, vcache, q_start, start_pos,      \
                          block_table, max_blocks, n_requests, max_tiles, n_heads, n_kv, hd, vd, page_size, window,    \
-                         scale, qt, chunk, max_splits, slopes, sinks, s)
+                         scale, qt, chunk, max_splits, slopes, sinks, segment, v_heads, v_row, out_f32, s)
     if (dtype == KLLM_F32) {
         if (vd <= 64) KLLM_SIMT(float, 1);
         if (vd <= 128) KLLM_SIMT(float, 2);
@@ -645,17 +668,19 @@ extern "C" int kllm_attention_simt(void* out, void* part_o, void* part_ml, const
 
 extern "C" int kllm_attention_simt_merge(void* out, const void* part_o, const void* part_ml, const int* positions,
                                          int n_tokens, int n_heads, int hd, int window, int chunk, int max_splits,
-                                         const float* sinks, int dtype, void* stream) {
+                                         const float* sinks, int segment, int out_f32, int dtype, void* stream) {
     if (n_tokens <= 0) return 0;
     if (hd <= 0 || hd > 256 || chunk <= 0 || max_splits < 1) KLLM_FAIL("attention merge (simt): bad sizes");
     cudaStream_t s = (cudaStream_t)stream;
     const int n_rows = n_tokens * n_heads;
     if (dtype == KLLM_F32)
         kllm_launch((attn_simt_merge_kernel<float>), dim3((n_rows + 3) / 4), dim3(128), 0, s, (float*)out,
-                    (const float*)part_o, (const float*)part_ml, positions, n_rows, n_heads, hd, window, chunk, max_splits, sinks);
+                    (const float*)part_o, (const float*)part_ml, positions, n_rows, n_heads, hd, window, chunk, max_splits, sinks,
+                    segment, out_f32);
     else if (dtype == KLLM_BF16)
         kllm_launch((attn_simt_merge_kernel<bf16>), dim3((n_rows + 3) / 4), dim3(128), 0, s, (bf16*)out,
-                    (const float*)part_o, (const float*)part_ml, positions, n_rows, n_heads, hd, window, chunk, max_splits, sinks);
+                    (const float*)part_o, (const float*)part_ml, positions, n_rows, n_heads, hd, window, chunk, max_splits, sinks,
+                    segment, out_f32);
     else
         KLLM_FAIL("attention merge (simt): unknown element type %d", dtype);
     KLLM_LAUNCH_STATUS();

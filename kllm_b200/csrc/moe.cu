@@ -3,6 +3,8 @@
 //   route     z = W_r h in float32 (h widened from the model's element type), score =
 //             sigmoid(z) or softmax(z); the `top` largest scores, the lower index first among
 //             equals; the weights are the chosen scores, as they are or divided by their sum.
+//             Optionally the experts form equal groups of neighbours, a group scores as its best
+//             expert, and only experts of the `keep` best groups can be chosen.
 //   sort      the (token, choice) pairs ordered by expert: offsets[E + 1] and perm[n * top]
 //             (sorted row -> token * top + choice), on the device, so that a step's launch
 //             shapes do not depend on the routing.
@@ -34,8 +36,8 @@ namespace {
 template <typename T>
 __global__ void __launch_bounds__(128)
 route_kernel(int* __restrict__ idx, float* __restrict__ wt, const T* __restrict__ h, const float* __restrict__ router,
-             int n, int d, int E, int top, int softmax, int renorm) {
-    extern __shared__ float zsh[];            // [4 warps][E]
+             int n, int d, int E, int top, int softmax, int renorm, int groups, int keep) {
+    extern __shared__ float zsh[];            // [4 warps][E], then [4 warps][2 * groups] when groups limit the choice
     griddep_wait();
     griddep_launch();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -61,6 +63,37 @@ route_kernel(int* __restrict__ idx, float* __restrict__ wt, const T* __restrict_
         zsum = 0.f;
         for (int e = lane; e < E; e += 32) zsum += expf(z[e] - zmax);
         zsum = warp_sum(zsum);
+    }
+    if (groups > 1 && keep < groups) {
+        // The experts form `groups` equal groups of neighbours; a group's score is its best expert's
+        // (the logits order as the scores do).  Only experts of the `keep` best groups can be chosen,
+        // the lower group first among equals; the scores themselves stay those over all experts.
+        float* gb = zsh + 4 * E + warp * 2 * groups;      // a group's best logit, then whether it is kept
+        const int per = E / groups;
+        for (int gi = lane; gi < groups; gi += 32) {
+            float b = -INFINITY;
+            for (int j = 0; j < per; j++) b = fmaxf(b, z[gi * per + j]);
+            gb[gi] = b;
+            gb[groups + gi] = 0.f;
+        }
+        __syncwarp();
+        for (int c = 0; c < keep; c++) {
+            float best = -INFINITY;
+            int bi = groups;
+            for (int gi = lane; gi < groups; gi += 32)
+                if (gb[groups + gi] == 0.f && (gb[gi] > best || bi == groups)) { best = gb[gi]; bi = gi; }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+                const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+                if (oi < groups && (bi == groups || ob > best || (ob == best && oi < bi))) { best = ob; bi = oi; }
+            }
+            if (lane == 0 && bi < groups) gb[groups + bi] = 1.f;
+            __syncwarp();
+        }
+        for (int e = lane; e < E; e += 32)
+            if (gb[groups + e / per] == 0.f) z[e] = -INFINITY;
+        __syncwarp();
     }
     float total = 0.f;
     for (int c = 0; c < top; c++) {
@@ -430,17 +463,20 @@ table_route_kernel(int* __restrict__ idx, float* __restrict__ wt, const int* __r
 
 // idx int32 [n][top], wt float32 [n][top]; h [n][d] contiguous in `dtype`; router float32 [E][d].
 extern "C" int kllm_moe_route(int* idx, float* wt, const void* h, const float* router, int n, int d, int E, int top,
-                              int softmax, int renorm, int dtype, void* stream) {
+                              int softmax, int renorm, int groups, int keep, int dtype, void* stream) {
     if (n <= 0) return 0;
     if (E <= 0 || E > 1024 || top <= 0 || top > E) KLLM_FAIL("moe route: %d of %d experts (at most 1024)", top, E);
+    if (groups < 1) groups = keep = 1;
+    if (E % groups || keep < 1 || keep > groups || top > keep * (E / groups))
+        KLLM_FAIL("moe route: %d of %d experts in %d groups of which %d are kept", top, E, groups, keep);
     cudaStream_t s = (cudaStream_t)stream;
-    const size_t smem = (size_t)4 * E * sizeof(float);
+    const size_t smem = (size_t)4 * (E + 2 * groups) * sizeof(float);
     if (dtype == KLLM_F32)
         kllm_launch((route_kernel<float>), dim3((n + 3) / 4), dim3(128), smem, s, idx, wt, (const float*)h, router, n, d, E,
-                    top, softmax, renorm);
+                    top, softmax, renorm, groups, keep);
     else if (dtype == KLLM_BF16)
         kllm_launch((route_kernel<bf16>), dim3((n + 3) / 4), dim3(128), smem, s, idx, wt, (const bf16*)h, router, n, d, E,
-                    top, softmax, renorm);
+                    top, softmax, renorm, groups, keep);
     else
         KLLM_FAIL("moe route: unknown element type %d", dtype);
     KLLM_LAUNCH_STATUS();

@@ -194,6 +194,53 @@ rmsnorm_add_kernel(float* __restrict__ x, const float* __restrict__ y, const flo
     for (int i = threadIdx.x; i < d; i += blockDim.x) orow[i] = from_f32<T>(xr[i] * scale2 * gain2[i]);
 }
 
+// Layer norm with gain and bias, the residual sum folded in as in add_rmsnorm_kernel:
+//
+//   x[r,:] (+)= res[r,:]
+//   out[r,:] = (x[r,:] - mean) * rsqrt(var + eps) * gain[:] + bias[:]
+//
+// mean and var (the mean of the squared deviations, taken about the mean in a second pass)
+// are float32.  One block per row whose size follows from the width alone, so a row's sums
+// have the same order whatever else the launch holds.  rows as in add_rmsnorm_kernel.
+template <typename T, typename R>
+__global__ void __launch_bounds__(kThreads)
+add_layernorm_kernel(float* __restrict__ x, const R* __restrict__ res, T* __restrict__ out,
+                     const float* __restrict__ gain, const float* __restrict__ bias, const int* __restrict__ rows,
+                     int d, float eps) {
+    __shared__ float red[32];
+    griddep_wait();
+    griddep_launch();
+    const int r = blockIdx.x;
+    const int64_t src = rows ? (int64_t)rows[r] : (int64_t)r;
+    float* xr = x + src * d;
+    const R* rr = res ? res + src * d : nullptr;
+    T* orow = out + (int64_t)r * d;
+    const bool write_back = (rows == nullptr) && (res != nullptr);
+    float sum = 0.f;
+    for (int i = threadIdx.x; i < d; i += blockDim.x) {
+        float v = xr[i];
+        if (rr) {
+            v += to_f32(rr[i]);
+            if (write_back) xr[i] = v;
+        }
+        sum += v;
+    }
+    const float mean = block_sum(sum, red) / (float)d;
+    float sq = 0.f;
+    for (int i = threadIdx.x; i < d; i += blockDim.x) {
+        float v = xr[i];
+        if (rr && !write_back) v += to_f32(rr[i]);
+        v -= mean;
+        sq += v * v;
+    }
+    const float scale = rsqrtf(block_sum(sq, red) / (float)d + eps);
+    for (int i = threadIdx.x; i < d; i += blockDim.x) {
+        float v = xr[i];
+        if (rr && !write_back) v += to_f32(rr[i]);
+        orow[i] = from_f32<T>((v - mean) * scale * gain[i] + bias[i]);
+    }
+}
+
 }  // namespace
 
 // x float32 [n][d] (updated), y float32 [n][d], gain float32 [d]; out (optional, element type
@@ -248,5 +295,26 @@ extern "C" int kllm_add_rmsnorm(void* x, const void* res, void* out, const void*
     } else {
         KLLM_FAIL("rmsnorm: element types %d (out) and %d (res) are not supported together", dtype, res_dtype);
     }
+    KLLM_LAUNCH_STATUS();
+}
+
+// Layer norm with gain and bias (both float32 [d]); the other arguments as in kllm_add_rmsnorm.
+extern "C" int kllm_add_layernorm(void* x, const void* res, void* out, const void* gain, const void* bias,
+                                  const int* rows, int n_rows, int d, float eps, int dtype, int res_dtype,
+                                  void* stream) {
+    if (n_rows <= 0) return 0;
+    if (d <= 0) KLLM_FAIL("layernorm: width %d must be positive", d);
+    if (!gain || !bias) KLLM_FAIL("layernorm: gain and bias are required");
+    cudaStream_t s = (cudaStream_t)stream;
+    const int threads = d <= 512 ? 64 : (d <= 2048 ? 128 : kThreads);
+    if (res == nullptr) res_dtype = dtype;
+#define KLLM_LN(T, R)                                                                                           \
+    kllm_launch((add_layernorm_kernel<T, R>), dim3(n_rows), dim3(threads), 0, s, (float*)x, (const R*)res, (T*)out, \
+                (const float*)gain, (const float*)bias, rows, d, eps)
+    if (dtype == KLLM_F32 && res_dtype == KLLM_F32) KLLM_LN(float, float);
+    else if (dtype == KLLM_BF16 && res_dtype == KLLM_BF16) KLLM_LN(bf16, bf16);
+    else if (dtype == KLLM_BF16 && res_dtype == KLLM_F32) KLLM_LN(bf16, float);
+    else KLLM_FAIL("layernorm: element types %d (out) and %d (res) are not supported together", dtype, res_dtype);
+#undef KLLM_LN
     KLLM_LAUNCH_STATUS();
 }

@@ -119,6 +119,29 @@ def add_rmsnorm(x: torch.Tensor, res: Optional[torch.Tensor], out: torch.Tensor,
     _check(lib, "norm", rc)
 
 
+def add_layernorm(x: torch.Tensor, res: Optional[torch.Tensor], out: torch.Tensor, gain: torch.Tensor,
+                  bias: torch.Tensor, eps: float, rows: Optional[torch.Tensor] = None) -> None:
+    """x (+)= res in float32, out = (x - mean) / sqrt(var + eps) * gain + bias; ``rows`` as in
+    ``add_rmsnorm`` (csrc/norm.cu)."""
+    _cuda(x, res, out, gain, bias, rows)
+    _i32(rows, "rows")
+    d = x.shape[1]
+    if x.dtype != torch.float32 or not x.is_contiguous() or not out.is_contiguous() or out.shape[1] != d:
+        raise KernelError("add_layernorm: x must be contiguous float32, out contiguous of the same width")
+    for t in (gain, bias):
+        if t.dtype != torch.float32 or t.numel() != d or not t.is_contiguous():
+            raise KernelError("add_layernorm: gain and bias must be contiguous float32 [d]")
+    if res is not None and (res.dtype not in (out.dtype, torch.float32) or not res.is_contiguous() or res.shape != x.shape):
+        raise KernelError("add_layernorm: res must match x in shape and be float32 or of out's dtype")
+    n_rows = out.shape[0]
+    if (rows is None and n_rows != x.shape[0]) or (rows is not None and rows.numel() != n_rows):
+        raise KernelError("add_layernorm: row counts do not agree")
+    lib = load_library("norm")
+    rc = lib.kllm_add_layernorm(_p(x), _p(res), _p(out), _p(gain), _p(bias), _p(rows), n_rows, d, ctypes.c_float(eps),
+                                dtype_code(out.dtype), dtype_code(res.dtype if res is not None else out.dtype), _stream())
+    _check(lib, "norm", rc)
+
+
 def rmsnorm_add(x: torch.Tensor, y: torch.Tensor, gain: torch.Tensor, eps: float,
                 out: Optional[torch.Tensor] = None, gain2: Optional[torch.Tensor] = None, eps2: float = 0.0) -> None:
     """x += rmsnorm(y) * gain, all float32 [n, d]: a norm on a sublayer's output as it joins
@@ -204,6 +227,122 @@ def latent_norm_append(q_out: torch.Tensor, proj: torch.Tensor, q_gain: torch.Te
     _check(lib, "latent", rc)
 
 
+def _f64(t: Optional[torch.Tensor], what: str):
+    if t is not None and (t.dtype != torch.float64 or not t.is_contiguous()):
+        raise KernelError(f"{what} must be a contiguous float64 tensor")
+
+
+def latent_rope_append(q_plain: torch.Tensor, q_full: torch.Tensor, proj: torch.Tensor, kv_gain: Optional[torch.Tensor],
+                       eps: float, freq: Optional[torch.Tensor], amplitude: float, positions: torch.Tensor,
+                       token_req: torch.Tensor, block_table: Optional[torch.Tensor], cache: Optional[torch.Tensor],
+                       n_heads: int, dk: int, dr: int, rank: int) -> None:
+    """What lies between the stacked projection and the attention of a layer that attends through a
+    latent plus one rotated key part (csrc/latent.cu): ``proj`` float32 [n, >= H (dk + dr) + R + dr]
+    holds per token the heads' queries (dk plain, dr rotated values each), the latent and the rotated
+    key part.  ``q_plain`` [n, H dk] gets the plain query values, ``q_full`` [n, H (R + dr)] the rotated
+    query parts in the tail of every head's row, the paged store ``cache`` [pages, 1, page_size,
+    R + dr] the RMS-normed latent times ``kv_gain`` and the rotated key part.  ``freq`` float64
+    [dr / 2]: pair (i, i + dr / 2) turns by position * freq[i]; cos and sin are multiplied by
+    ``amplitude``.  With ``cache`` None only the queries are produced."""
+    _cuda(q_plain, q_full, proj, kv_gain, freq, positions, token_req, block_table, cache)
+    _i32(positions, "positions"); _i32(token_req, "token_req"); _i32(block_table, "block_table"); _f64(freq, "freq")
+    n = proj.shape[0]
+    if proj.dtype != torch.float32 or proj.stride(1) != 1 or proj.shape[1] < n_heads * (dk + dr) + rank + dr:
+        raise KernelError("latent_rope_append: the projections must be float32 [n, >= H (dk + dr) + R + dr] with dense rows")
+    if (tuple(q_plain.shape) != (n, n_heads * dk) or tuple(q_full.shape) != (n, n_heads * (rank + dr))
+            or not q_plain.is_contiguous() or not q_full.is_contiguous() or q_plain.dtype != q_full.dtype):
+        raise KernelError("latent_rope_append: q_plain [n, H dk] and q_full [n, H (R + dr)] contiguous, of one dtype")
+    if dr and (freq is None or freq.numel() != dr // 2):
+        raise KernelError("latent_rope_append: one frequency per rotated pair")
+    page_size = max_blocks = 0
+    if cache is not None:
+        page_size, max_blocks = cache.shape[2], block_table.shape[1]
+        if cache.dtype != q_plain.dtype or not cache.is_contiguous() or cache.shape[1] != 1 or cache.shape[3] != rank + dr:
+            raise KernelError("latent_rope_append: the store must be contiguous [pages, 1, page_size, R + dr] in q's dtype")
+        if kv_gain is None or kv_gain.dtype != torch.float32 or kv_gain.numel() != rank or not kv_gain.is_contiguous():
+            raise KernelError("latent_rope_append: the latent's gain must be float32 [R]")
+    lib = load_library("latent")
+    rc = lib.kllm_latent_rope_append(_p(q_plain), _p(q_full), _p(proj), ctypes.c_int64(proj.stride(0)), _p(kv_gain),
+                                     ctypes.c_float(eps), _p(freq), ctypes.c_float(amplitude), _p(positions),
+                                     _p(token_req), _p(block_table), max_blocks, _p(cache), n, n_heads, dk, dr, rank,
+                                     page_size, dtype_code(q_plain.dtype), _stream())
+    _check(lib, "latent", rc)
+
+
+def headnorm_rope_append(q_out: torch.Tensor, qkv: torch.Tensor, bias: Optional[torch.Tensor],
+                         q_gain: Optional[torch.Tensor], k_gain: Optional[torch.Tensor], eps: float,
+                         freq: Optional[torch.Tensor], amplitude: float, rot: int, positions: torch.Tensor,
+                         token_req: torch.Tensor, block_table: Optional[torch.Tensor], kcache: Optional[torch.Tensor],
+                         vcache: Optional[torch.Tensor], q_heads: int, k_heads: int, v_heads: int, dk: int, dv: int) -> None:
+    """Bias, RMS norm per head with a gain [dk] that all heads share, rotation of the first ``rot`` values
+    of every query and key head, and the cache write, in one kernel (csrc/qk_headnorm.cu).  ``qkv`` float32
+    [n, (q_heads + k_heads) dk + v_heads dv]; ``bias`` float32 of a row's length or None; ``q_gain`` /
+    ``k_gain`` float32 [dk] or None (no norm); ``freq`` float64 [rot / 2] (pair (i, i + rot / 2) turns by
+    position * freq[i], cos and sin times ``amplitude``); ``q_out`` [n, q_heads dk] in the model dtype;
+    caches [pages, k_heads, page_size, dk] and [pages, v_heads, page_size, dv].  With ``kcache`` None ``qkv``
+    holds queries only."""
+    _cuda(q_out, qkv, bias, q_gain, k_gain, freq, positions, token_req, block_table, kcache, vcache)
+    _i32(positions, "positions"); _i32(token_req, "token_req"); _i32(block_table, "block_table"); _f64(freq, "freq")
+    n = qkv.shape[0]
+    width = q_heads * dk + ((k_heads * dk + v_heads * dv) if kcache is not None else 0)
+    if qkv.dtype != torch.float32 or qkv.stride(1) != 1 or qkv.shape[1] < width:
+        raise KernelError("headnorm_rope_append: the projections must be float32 with dense rows of q, k and v")
+    if tuple(q_out.shape) != (n, q_heads * dk) or not q_out.is_contiguous():
+        raise KernelError("headnorm_rope_append: q_out must be contiguous [n, q_heads * dk]")
+    if bias is not None and (bias.dtype != torch.float32 or not bias.is_contiguous() or bias.numel() < width):
+        raise KernelError("headnorm_rope_append: the bias must be float32 of a row's length")
+    for g in (q_gain, k_gain):
+        if g is not None and (g.dtype != torch.float32 or not g.is_contiguous() or g.numel() != dk):
+            raise KernelError("headnorm_rope_append: a gain must be float32 [dk]")
+    if rot and (freq is None or freq.numel() != rot // 2):
+        raise KernelError("headnorm_rope_append: one frequency per rotated pair")
+    page_size = max_blocks = 0
+    if kcache is not None:
+        page_size, max_blocks = kcache.shape[2], block_table.shape[1]
+        if (kcache.dtype != q_out.dtype or vcache.dtype != q_out.dtype or not kcache.is_contiguous()
+                or not vcache.is_contiguous() or tuple(kcache.shape[1:]) != (k_heads, page_size, dk)
+                or tuple(vcache.shape[1:]) != (v_heads, page_size, dv) or vcache.shape[0] != kcache.shape[0]):
+            raise KernelError("headnorm_rope_append: caches must be [pages, heads, page_size, size] in q_out's dtype")
+    lib = load_library("qk_headnorm")
+    rc = lib.kllm_headnorm_rope_append(_p(q_out), _p(qkv), ctypes.c_int64(qkv.stride(0)), _p(bias), _p(q_gain), _p(k_gain),
+                                       ctypes.c_float(eps), _p(freq), ctypes.c_float(amplitude), int(rot), _p(positions),
+                                       _p(token_req), _p(block_table), max_blocks, _p(kcache), _p(vcache), n, q_heads,
+                                       k_heads, v_heads, dk, dv, page_size, dtype_code(q_out.dtype), _stream())
+    _check(lib, "qk_headnorm", rc)
+
+
+def maps_combine(out: torch.Tensor, a: torch.Tensor, kv_heads: int, group: int, dv: int, lam: float, eps: float,
+                 post: float) -> None:
+    """out [n, G gs dv] = (a1 - lam a2) / rms(a1 - lam a2 over dv) * post for every head, from the two
+    attention maps of a differential attention: ``a`` float32 [n, G, 2, gs, dv] (csrc/qk_headnorm.cu)."""
+    _cuda(out, a)
+    n = a.shape[0]
+    if a.dtype != torch.float32 or not a.is_contiguous() or a.shape[1] != kv_heads * 2 * group * dv:
+        raise KernelError("maps_combine: the maps must be contiguous float32 [n, G * 2 * gs * dv]")
+    if tuple(out.shape) != (n, kv_heads * group * dv) or not out.is_contiguous():
+        raise KernelError("maps_combine: out must be contiguous [n, G * gs * dv]")
+    lib = load_library("qk_headnorm")
+    rc = lib.kllm_maps_combine(_p(out), _p(a), n, kv_heads, group, dv, ctypes.c_float(lam), ctypes.c_float(eps),
+                               ctypes.c_float(post), dtype_code(out.dtype), _stream())
+    _check(lib, "qk_headnorm", rc)
+
+
+def sigmoid_gate(out: torch.Tensor, a: torch.Tensor, gate: torch.Tensor) -> None:
+    """out = a * sigmoid(gate): a and out in the model dtype, gate float32 logits; dense rows, strided rows
+    allowed (csrc/activation.cu)."""
+    _cuda(out, a, gate)
+    if gate.dtype != torch.float32 or a.dtype != out.dtype or a.shape != out.shape or gate.shape != out.shape:
+        raise KernelError("sigmoid_gate: a and out of one dtype and shape, gate float32 of that shape")
+    for t in (out, a, gate):
+        if t.stride(1) != 1:
+            raise KernelError("sigmoid_gate: operands must have dense rows")
+    n, f = out.shape
+    lib = load_library("activation")
+    rc = lib.kllm_sigmoid_gate(_p(out), ctypes.c_int64(out.stride(0)), _p(a), ctypes.c_int64(a.stride(0)), _p(gate),
+                               ctypes.c_int64(gate.stride(0)), n, f, dtype_code(out.dtype), _stream())
+    _check(lib, "activation", rc)
+
+
 def streams_step(streams: torch.Tensor, *, init: Optional[torch.Tensor] = None, y: Optional[torch.Tensor] = None,
                  mix: Optional[torch.Tensor] = None, out_w: Optional[torch.Tensor] = None,
                  in_w: Optional[torch.Tensor] = None, gain: Optional[torch.Tensor] = None, eps: float = 0.0,
@@ -270,17 +409,20 @@ def attention_generic(out: torch.Tensor, q: torch.Tensor, kcache: torch.Tensor, 
                       positions: torch.Tensor, token_req: torch.Tensor, block_table: torch.Tensor,
                       n_heads: int, n_kv: int, head_dim: int, window: int, scale: float,
                       score_slopes: Optional[torch.Tensor] = None, v_head_dim: Optional[int] = None,
-                      sinks: Optional[torch.Tensor] = None) -> None:
+                      sinks: Optional[torch.Tensor] = None, segment: int = 0) -> None:
     """Causal GQA attention of every new token over its request's cached keys: one warp per
     (token, head), any head size up to 512, values of their own size, optional score slopes and
-    sinks (float32 [n_heads]: exp(sinks[h]) joins the denominator of head h's softmax)."""
+    sinks (float32 [n_heads]: exp(sinks[h]) joins the denominator of head h's softmax).
+    ``segment``, fewer value heads than key heads, value rows that head longer rows and a float32
+    ``out`` as in ``attention_simt``."""
     _cuda(out, q, kcache, vcache, positions, token_req, block_table, score_slopes, sinks)
     vd = int(v_head_dim or head_dim)
-    if vcache.shape[3] != vd or vcache.shape[:3] != kcache.shape[:3] or out.shape[1] != n_heads * vd:
-        raise KernelError("attention: value cache [pages, n_kv, page_size, value size] and out [n, heads * value size]")
+    v_heads, v_row = _value_layout(kcache, vcache, n_kv, vd)
+    if out.shape[1] != n_heads * vd:
+        raise KernelError("attention: out must be [n, heads * value size]")
     _i32(positions, "positions"); _i32(token_req, "token_req"); _i32(block_table, "block_table")
-    if q.stride(1) != 1 or not out.is_contiguous() or out.dtype != q.dtype or kcache.dtype != q.dtype:
-        raise KernelError("attention: operands must share a dtype; out contiguous, q rows dense")
+    if q.stride(1) != 1 or not out.is_contiguous() or out.dtype not in (q.dtype, torch.float32) or kcache.dtype != q.dtype:
+        raise KernelError("attention: operands must share a dtype; out contiguous (of that dtype or float32), q rows dense")
     if not kcache.is_contiguous() or not vcache.is_contiguous() or kcache.shape[1] != n_kv or kcache.shape[3] != head_dim:
         raise KernelError("attention: cache layout must be [pages, n_kv, page_size, head_dim]")
     n = q.shape[0]
@@ -289,8 +431,22 @@ def attention_generic(out: torch.Tensor, q: torch.Tensor, kcache: torch.Tensor, 
                                     _p(positions), _p(token_req), _p(block_table), block_table.shape[1],
                                     n, n_heads, n_kv, head_dim, vd, kcache.shape[2], int(window or 0),
                                     ctypes.c_float(scale), _slopes_arg(score_slopes, n_heads),
-                                    _slopes_arg(sinks, n_heads, "sinks"), dtype_code(q.dtype), _stream())
+                                    _slopes_arg(sinks, n_heads, "sinks"), int(segment or 0), v_heads, v_row,
+                                    int(out.dtype == torch.float32 and q.dtype != torch.float32), dtype_code(q.dtype),
+                                    _stream())
     _check(lib, "attention_generic", rc)
+
+
+def _value_layout(kcache, vcache, n_kv, vd):
+    """(value heads, elements between value rows) of a value store [pages, value heads, page_size, row]
+    beside a key store [pages, n_kv, page_size, head_dim]: the value heads divide the key heads, a
+    row holds at least ``vd`` values (more when the values head a longer row)."""
+    if (vcache.dim() != 4 or vcache.shape[0] != kcache.shape[0] or vcache.shape[2] != kcache.shape[2]
+            or vcache.shape[1] <= 0 or n_kv % vcache.shape[1] or vcache.shape[3] < vd or not vcache.is_contiguous()
+            or vcache.dtype != kcache.dtype):
+        raise KernelError("attention: value store [pages, value heads, page_size, >= value size], its heads dividing "
+                          "the key heads")
+    return int(vcache.shape[1]), int(vcache.shape[3])
 
 
 SIMT_CHUNK = 256      # keys per CTA when a decoding token's context is cut (attention_simt)
@@ -299,7 +455,7 @@ SIMT_CHUNK = 256      # keys per CTA when a decoding token's context is cut (att
 def attention_simt(out: torch.Tensor, q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, ctx,
                    block_table: torch.Tensor, n_heads: int, n_kv: int, head_dim: int, window: int,
                    scale: float, score_slopes: Optional[torch.Tensor] = None, v_head_dim: Optional[int] = None,
-                   sinks: Optional[torch.Tensor] = None) -> None:
+                   sinks: Optional[torch.Tensor] = None, segment: int = 0) -> None:
     """Causal GQA attention of the step's tokens on the CUDA cores, float32 arithmetic
     (csrc/attention_simt.cu): the attention of the float32 path.  The requests that bring
     one token each at the head of the batch (decoding requests, which the scheduler puts
@@ -309,18 +465,26 @@ def attention_simt(out: torch.Tensor, q: torch.Tensor, kcache: torch.Tensor, vca
     to the scaled scores of head h.  ``v_head_dim``: the size of a head's values and of its
     output where it differs from the keys' (``vcache`` [pages, n_kv, page_size, v_head_dim],
     ``out`` [n, n_heads * v_head_dim]).  ``sinks`` (float32 [n_heads]): exp(sinks[h]) is one more
-    term of the denominator of head h's softmax, without a key or a value."""
+    term of the denominator of head h's softmax, without a key or a value.  ``segment`` C: positions
+    are cut into segments of C counted from 0 and a query sees only the keys of its own segment.
+    The value store may have fewer heads than the key store (``vcache`` [pages, v_heads, page_size,
+    row]: n_kv / v_heads neighbouring key heads read one value head) and rows longer than
+    ``v_head_dim`` (the values are then the head of each row: a store whose rows are keys and, in
+    their first part, values).  ``out`` may be float32 beside bfloat16 operands."""
     _cuda(out, q, kcache, vcache, block_table, score_slopes, sinks)
     _slopes_arg(sinks, n_heads, "sinks")
     vd = int(v_head_dim or head_dim)
+    v_heads, v_row = _value_layout(kcache, vcache, n_kv, vd)
+    segment = int(segment or 0)
+    out_f32 = int(out.dtype == torch.float32 and q.dtype != torch.float32)
     if score_slopes is not None and (score_slopes.dtype != torch.float32 or not score_slopes.is_contiguous()
                                      or score_slopes.numel() != n_heads):
         raise KernelError("attention: score slopes must be a contiguous float32 tensor, one per head")
     _i32(block_table, "block_table"); _i32(ctx.q_start, "q_start"); _i32(ctx.start_pos, "start_pos")
-    if q.stride(1) != 1 or not out.is_contiguous() or out.dtype != q.dtype or kcache.dtype != q.dtype:
-        raise KernelError("attention: operands must share a dtype; out contiguous, q rows dense")
-    if not kcache.is_contiguous() or not vcache.is_contiguous() or kcache.shape[1] != n_kv or kcache.shape[3] != head_dim \
-            or vcache.shape[3] != vd or vcache.shape[:3] != kcache.shape[:3] or out.shape[1] != n_heads * vd:
+    if q.stride(1) != 1 or not out.is_contiguous() or out.dtype not in (q.dtype, torch.float32) or kcache.dtype != q.dtype:
+        raise KernelError("attention: operands must share a dtype; out contiguous (of that dtype or float32), q rows dense")
+    if not kcache.is_contiguous() or kcache.shape[1] != n_kv or kcache.shape[3] != head_dim \
+            or out.shape[1] != n_heads * vd or v_row % 4:
         raise KernelError("attention: cache layout must be [pages, n_kv, page_size, head_dim]")
     group = n_heads // max(1, n_kv)
     lib = load_library("attention_simt")
@@ -332,6 +496,8 @@ def attention_simt(out: torch.Tensor, q: torch.Tensor, kcache: torch.Tensor, vca
     bound = ctx.split_bound or ctx.max_ctx
     if window:
         bound = min(bound, int(window))
+    if segment:
+        bound = min(bound, segment)
     splits = max(1, -(-bound // SIMT_CHUNK))
     common = (n_heads, n_kv, head_dim, vd, kcache.shape[2], int(window or 0), ctypes.c_float(scale))
     first = 0
@@ -342,11 +508,12 @@ def attention_simt(out: torch.Tensor, q: torch.Tensor, kcache: torch.Tensor, vca
         rc = lib.kllm_attention_simt(_p(out), _p(part_o), _p(part_ml), _p(q), ctypes.c_int64(q.stride(0)), _p(kcache),
                                      _p(vcache), _p(ctx.q_start), _p(ctx.start_pos), _p(block_table),
                                      block_table.shape[1], singles, singles, *common, 1, SIMT_CHUNK, splits,
-                                     _p(score_slopes), _p(sinks), dtype_code(q.dtype), _stream())
+                                     _p(score_slopes), _p(sinks), segment, v_heads, v_row, out_f32, dtype_code(q.dtype),
+                                     _stream())
         _check(lib, "attention_simt", rc)
         rc = lib.kllm_attention_simt_merge(_p(out), _p(part_o), _p(part_ml), _p(ctx.positions), singles, n_heads,
-                                           vd, int(window or 0), SIMT_CHUNK, splits, _p(sinks), dtype_code(q.dtype),
-                                           _stream())
+                                           vd, int(window or 0), SIMT_CHUNK, splits, _p(sinks), segment, out_f32,
+                                           dtype_code(q.dtype), _stream())
         _check(lib, "attention_simt", rc)
         first = singles
     if first < n_req:
@@ -355,7 +522,8 @@ def attention_simt(out: torch.Tensor, q: torch.Tensor, kcache: torch.Tensor, vca
         rc = lib.kllm_attention_simt(_p(out), None, None, _p(q), ctypes.c_int64(q.stride(0)), _p(kcache), _p(vcache),
                                      _p(ctx.q_start[first:]), _p(ctx.start_pos[first:]), _p(block_table[first:]),
                                      block_table.shape[1], n_req - first, rest // qt + (n_req - first), *common, qt, 0, 1,
-                                     _p(score_slopes), _p(sinks), dtype_code(q.dtype), _stream())
+                                     _p(score_slopes), _p(sinks), segment, v_heads, v_row, out_f32, dtype_code(q.dtype),
+                                     _stream())
         _check(lib, "attention_simt", rc)
 
 
@@ -408,7 +576,7 @@ def decode_splits(n_tokens: int, n_kv: int, ctx_bound: int) -> int:
 def attention(out: torch.Tensor, q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, ctx,
               block_table: torch.Tensor, n_heads: int, n_kv: int, head_dim: int, window: int,
               scale: float, score_slopes: Optional[torch.Tensor] = None, v_head_dim: Optional[int] = None,
-              exact_weights: bool = False, sinks: Optional[torch.Tensor] = None) -> None:
+              exact_weights: bool = False, sinks: Optional[torch.Tensor] = None, segment: int = 0) -> None:
     """Causal GQA attention of the step's tokens over the paged cache, by the
     kernel that fits: bfloat16 with a head size in TC_HEAD_DIMS runs on tensor cores
     (the decode form when every request brings one token, else the prefill form: on
@@ -426,20 +594,24 @@ def attention(out: torch.Tensor, q: torch.Tensor, kcache: torch.Tensor, vcache: 
     two bfloat16 terms (16 bits of mantissa), the CUDA-core kernel as float32.  Values of
     another size than the keys (``v_head_dim``) are taken by the CUDA-core kernel alone.
     ``sinks`` (float32 [n_heads]): exp(sinks[h]) joins the denominator of head h's softmax, a
-    term without a key or a value; taken by the CUDA-core kernels and the ``mma.sync`` kernels."""
+    term without a key or a value; taken by the CUDA-core kernels and the ``mma.sync`` kernels.
+    ``segment`` (a query sees only the keys of its own segment of that many positions), a value
+    store with fewer heads than the key store or with rows that the values only head, and a
+    float32 ``out`` beside bfloat16 operands are taken by the CUDA-core kernels."""
     group = n_heads // max(1, n_kv)
     vd = int(v_head_dim or head_dim)
     special = score_slopes is not None or exact_weights
     special = special or sinks is not None
+    plain_values = vcache.shape[1] == n_kv and vcache.shape[3] == vd and out.dtype == q.dtype
     tc = (q.dtype == torch.bfloat16 and (head_dim in TC_HEAD_DIMS or head_dim in TC_WIDE_HEAD_DIMS) and vd == head_dim
-          and not (special and scale <= 0))
-    if (special or vd != head_dim) and not (tc and group <= 64):
-        if not simt_fits(q, n_heads, n_kv, head_dim, vd):
+          and not (special and scale <= 0) and not segment and plain_values)
+    if (special or vd != head_dim or segment or not plain_values) and not (tc and group <= 64):
+        if not simt_fits(q, n_heads, n_kv, head_dim, vd) or vcache.shape[3] % 4:
             # head sizes that are no multiples of 4, very wide groups: one warp per (token, head)
             return attention_generic(out, q, kcache, vcache, ctx.positions, ctx.token_req, block_table, n_heads, n_kv,
-                                     head_dim, window, scale, score_slopes, vd, sinks)
+                                     head_dim, window, scale, score_slopes, vd, sinks, segment)
         return attention_simt(out, q, kcache, vcache, ctx, block_table, n_heads, n_kv, head_dim, window, scale,
-                              score_slopes, vd, sinks)
+                              score_slopes, vd, sinks, segment)
     # the decode kernel takes 16 heads per CTA: more heads on a kv head are cut into groups of equal size
     groups = n_kv * next(s for s in range(1, group + 1) if group % s == 0 and group // s <= 16)
     if tc and ctx.all_single and group <= 64:
@@ -993,7 +1165,8 @@ def linear_batched(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
     return torch.stack([torch.mm(x[i], wt[i], out_dtype=torch.float32) for i in range(x.shape[0])])
 
 
-def linear_per_head(x: torch.Tensor, weight: torch.Tensor, transposed: bool = False) -> torch.Tensor:
+def linear_per_head(x: torch.Tensor, weight: torch.Tensor, transposed: bool = False,
+                    out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """y[t, h, :] = weight[h] @ x[t, h, :] for every head h: x [n, H * a] contiguous, weight
     [H, b, a] (``transposed``: weight [H, a, b], used as weight[h]^T), y [n, H * b] in x's dtype.
     One batched product of the vendor GEMM library over the heads, reading x and writing y in
@@ -1007,6 +1180,16 @@ def linear_per_head(x: torch.Tensor, weight: torch.Tensor, transposed: bool = Fa
     b = weight.shape[2] if transposed else weight.shape[1]
     if x.dtype != weight.dtype or not x.is_contiguous() or x.shape[1] != H * a:
         raise KernelError("linear_per_head: x must be contiguous [n, heads * a] in the weights' dtype")
+    if out is not None:
+        # the heads' results into a view [n, H, b] of a wider row (rows dense in b)
+        if tuple(out.shape) != (n, H, b) or out.dtype != x.dtype or out.stride(2) != 1:
+            raise KernelError("linear_per_head: out must be a view [n, heads, b] in x's dtype with dense rows")
+        y3 = out.transpose(0, 1)
+        if out.stride(0) % 8 == 0 and out.stride(1) % 8 == 0 and out.data_ptr() % 16 == 0:
+            torch.bmm(x.view(n, H, a).transpose(0, 1), weight if transposed else weight.transpose(1, 2), out=y3)
+        else:
+            y3.copy_(torch.bmm(x.view(n, H, a).transpose(0, 1), weight if transposed else weight.transpose(1, 2)))
+        return out
     y = torch.empty((n, H * b), dtype=x.dtype, device=x.device)
     torch.bmm(x.view(n, H, a).transpose(0, 1), weight if transposed else weight.transpose(1, 2),
               out=y.view(n, H, b).transpose(0, 1))
@@ -1142,9 +1325,12 @@ def unary(x: torch.Tensor, op: str, dtype: torch.dtype) -> torch.Tensor:
 
 _GATED_ACT = {"silu": 0, "clamped": 1}
 
-def moe_route(h: torch.Tensor, router: torch.Tensor, top: int, score: str = "sigmoid", renormalize: bool = False):
+def moe_route(h: torch.Tensor, router: torch.Tensor, top: int, score: str = "sigmoid", renormalize: bool = False,
+              groups: int = 1, keep: int = 1):
     """(idx int32 [n, top], weights float32 [n, top]): logits router @ h in float32, scores by
-    ``score`` ("sigmoid" or "softmax"), the ``top`` largest, the lower index among equals."""
+    ``score`` ("sigmoid" or "softmax"), the ``top`` largest, the lower index among equals.  With
+    ``groups`` > 1 the experts form that many equal groups of neighbours, a group scores as its best
+    expert, and only experts of the ``keep`` best groups can be chosen."""
     _cuda(h, router)
     n, d = h.shape
     if not h.is_contiguous() or router.dtype != torch.float32 or not router.is_contiguous() or router.shape[1] != d:
@@ -1155,7 +1341,8 @@ def moe_route(h: torch.Tensor, router: torch.Tensor, top: int, score: str = "sig
     wt = torch.empty((n, top), dtype=torch.float32, device=h.device)
     lib = load_library("moe")
     rc = lib.kllm_moe_route(_p(idx), _p(wt), _p(h), _p(router), n, d, router.shape[0], int(top),
-                            int(score == "softmax"), int(bool(renormalize)), dtype_code(h.dtype), _stream())
+                            int(score == "softmax"), int(bool(renormalize)), int(groups or 1), int(keep or 1),
+                            dtype_code(h.dtype), _stream())
     _check(lib, "moe", rc)
     return idx, wt
 

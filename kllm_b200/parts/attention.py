@@ -21,6 +21,17 @@ A ``qk_transform`` that offers ``prepare(qkv, ctx, cache, attention) -> q`` is g
 float32 result of the stacked projection instead: it returns the queries in the model dtype
 and writes keys and values into the cache itself (one kernel between the product and the
 attention, as the rotary kernel is for Llama); it needs ``position`` None.
+``segment`` (C: positions are cut into segments of C counted from 0 of the sequence, and a query
+sees only the earlier keys of its own segment), ``bias`` (True: q, k and v have biases, tensors
+``<weight name>.b`` or ``tensors`` entries q_bias / k_bias / v_bias, float32, handed to a
+``qk_transform`` with ``prepare``, which adds them), ``differential`` (a dict {``diff``, ``eps``,
+``tensors``: lq1, lk1, lq2, lk2 -> full names of float32 vectors [head_dim]}: every head has TWO
+attention maps over the same values, q [H * 2 * hd] and k [G * 2 * hd] laid out head by head as
+[map 1, map 2]; with lambda = exp(lq1 . lk1) - exp(lq2 . lk2) + diff the head's output is
+a1 - lambda a2, divided by its root mean square over the head's values (eps inside the root) and
+multiplied by 1 - diff.  The two maps run as 2H query heads over 2G key heads and G value heads,
+the queries' rows reordered when the weights are bound so that the heads of a key head are
+neighbours; the maps' outputs stay float32 until they are combined).
 Tensors: ``<prefix>.{q,k,v,o}_proj.weight`` with shapes [H*hd, d], [G*hd, d],
 [G*vd, d], [d, H*vd]; no bias (reference backend/model.cu:1090-1104).  At bind time
 q, k and v are stacked into one [(H+2G)*hd, d] matrix so the three projections are
@@ -63,8 +74,12 @@ class PagedAttention:
         self.scale = float(p.get("scale") or 1.0 / math.sqrt(self.head_dim))
         self.v_head_dim = int(p.get("v_head_dim") or self.head_dim)
         self.exact_weights = bool(p.get("exact_weights", False))
-        self.q_dim = self.n_heads * self.head_dim
-        self.kv_dim = self.n_kv * self.head_dim
+        self.segment = int(p.get("segment") or 0)
+        self.has_bias = bool(p.get("bias", False))
+        self.differential = p.get("differential")
+        self.maps = 2 if self.differential else 1
+        self.q_dim = self.n_heads * self.maps * self.head_dim
+        self.kv_dim = self.n_kv * self.maps * self.head_dim
         self.v_dim = self.n_kv * self.v_head_dim
         self.o_dim = self.n_heads * self.v_head_dim
         self.prefix = spec.prefix
@@ -77,6 +92,11 @@ class PagedAttention:
         self._prepares = hasattr(self.qk_transform, "prepare")
         if self._prepares and pos is not None:
             raise ValueError("attention: a qk_transform that stores keys and values goes without a position part")
+        if (self.has_bias or self.differential) and not self._prepares:
+            raise ValueError("attention: biases and differential maps need a qk_transform that takes the float32 "
+                             "projections (prepare)")
+        self.bias = None
+        self.lam = 0.0
         slopes = p.get("score_slopes")
         if slopes == "geometric":
             # the slopes 2^(-8 (h + 1) / H) of a bias that grows with the distance, head by head
@@ -95,29 +115,58 @@ class PagedAttention:
         self._after = []           # weights streamed right after this part (see set_prefetch_targets)
 
     def _names(self):
-        return {k: self.names.get(k) or f"{self.prefix}.{k}_proj.weight" for k in "qkvo"}
+        n = {k: self.names.get(k) or f"{self.prefix}.{k}_proj.weight" for k in "qkvo"}
+        for k in "qkv":
+            n[k + "_bias"] = self.names.get(k + "_bias") or n[k] + ".b"
+        return n
 
     def tensor_specs(self):
         n = self._names()
-        return [TensorSpec(n["q"], (self.q_dim, self.hidden)),
-                TensorSpec(n["k"], (self.kv_dim, self.hidden)),
-                TensorSpec(n["v"], (self.v_dim, self.hidden)),
-                TensorSpec(n["o"], (self.hidden, self.o_dim))] + \
-            (self.position.tensor_specs() if self.position else []) + \
+        out = [TensorSpec(n["q"], (self.q_dim, self.hidden)),
+               TensorSpec(n["k"], (self.kv_dim, self.hidden)),
+               TensorSpec(n["v"], (self.v_dim, self.hidden)),
+               TensorSpec(n["o"], (self.hidden, self.o_dim))]
+        if self.has_bias:
+            out += [TensorSpec(n["q_bias"], (self.q_dim,), store="float32", init="normal"),
+                    TensorSpec(n["k_bias"], (self.kv_dim,), store="float32", init="normal"),
+                    TensorSpec(n["v_bias"], (self.v_dim,), store="float32", init="normal")]
+        if self.differential:
+            out += [TensorSpec(self.differential["tensors"][k], (self.head_dim,), store="float32", init="normal")
+                    for k in ("lq1", "lk1", "lq2", "lk2")]
+        return out + (self.position.tensor_specs() if self.position else []) + \
             (self.qk_transform.tensor_specs() if self.qk_transform else [])
+
+    def _by_key_head(self, t):
+        """Rows of a query tensor [H * maps * hd, ...] laid out head by head as [map 1, map 2], reordered to
+        [kv head][map][head of the group]: the heads that share a key head (of one map) become neighbours."""
+        if self.maps == 1:
+            return t
+        gs = self.n_heads // self.n_kv
+        rest = tuple(t.shape[1:])
+        t = t.reshape((self.n_kv, gs, self.maps, self.head_dim) + rest)
+        return t.transpose(1, 2).reshape((self.q_dim,) + rest)
 
     def bind(self, tensors):
         n = self._names()
-        self.w_qkv = torch.cat([tensors[n["q"]], tensors[n["k"]], tensors[n["v"]]], dim=0).contiguous()
+        self.w_qkv = torch.cat([self._by_key_head(tensors[n["q"]]), tensors[n["k"]], tensors[n["v"]]], dim=0).contiguous()
         self.w_o = tensors[n["o"]]
+        if self.has_bias:
+            self.bias = torch.cat([self._by_key_head(tensors[n["q_bias"]]), tensors[n["k_bias"]],
+                                   tensors[n["v_bias"]]]).contiguous()
+        if self.differential:
+            import math
+            v = {k: tensors[self.differential["tensors"][k]].double() for k in ("lq1", "lk1", "lq2", "lk2")}
+            self.lam = (math.exp(float((v["lq1"] * v["lk1"]).sum())) - math.exp(float((v["lq2"] * v["lk2"]).sum()))
+                        + float(self.differential["diff"]))
         if self.position:
             self.position.bind(tensors)
         if self.qk_transform:
             self.qk_transform.bind(tensors)
 
     def cache_need(self):
-        return PagedKVNeed(self.n_kv, self.head_dim, self.window,
-                           None if self.v_head_dim == self.head_dim else self.v_head_dim)
+        return PagedKVNeed(self.n_kv * self.maps, self.head_dim, self.window,
+                           None if self.v_head_dim == self.head_dim else self.v_head_dim,
+                           n_v_heads=self.n_kv if self.maps > 1 else None)
 
     def _split(self, qkv, writes):
         q = qkv[:, :self.q_dim]
@@ -145,10 +194,21 @@ class PagedAttention:
         """The route of a ``qk_transform`` with ``prepare``: it takes the float32 projections,
         returns q and has stored k and v."""
         q = self.qk_transform.prepare(qkv, ctx, cache, self)
-        attn = torch.empty((q.shape[0], self.o_dim), dtype=self.dtype, device=q.device)
-        kernels.attention(attn, q, cache.k, cache.v, ctx, cache.block_table, self.n_heads, self.n_kv,
-                          self.head_dim, self.window or 0, self.scale, score_slopes=self.score_slopes,
-                          v_head_dim=self.v_head_dim, exact_weights=self.exact_weights)
+        n = q.shape[0]
+        attn = torch.empty((n, self.o_dim), dtype=self.dtype, device=q.device)
+        if self.maps == 1:
+            kernels.attention(attn, q, cache.k, cache.v, ctx, cache.block_table, self.n_heads, self.n_kv,
+                              self.head_dim, self.window or 0, self.scale, score_slopes=self.score_slopes,
+                              v_head_dim=self.v_head_dim, exact_weights=self.exact_weights, segment=self.segment)
+            return attn
+        # two maps per head: 2H query heads over 2G key heads and G value heads, combined afterwards
+        both = torch.empty((n, self.maps * self.o_dim), dtype=torch.float32, device=q.device)
+        kernels.attention(both, q, cache.k, cache.v, ctx, cache.block_table, self.n_heads * self.maps,
+                          self.n_kv * self.maps, self.head_dim, self.window or 0, self.scale,
+                          score_slopes=self.score_slopes, v_head_dim=self.v_head_dim, exact_weights=True,
+                          segment=self.segment)
+        kernels.maps_combine(attn, both, self.n_kv, self.n_heads // self.n_kv, self.v_head_dim, self.lam,
+                             float(self.differential["eps"]), 1.0 - float(self.differential["diff"]))
         return attn
 
     def _attend(self, q, k, v, ctx, cache, prefetch=None):
@@ -158,8 +218,8 @@ class PagedAttention:
         if self.qk_transform is not None:
             self.qk_transform.apply(q, k if cache.writes else None, ctx, self.n_heads, self.n_kv, self.head_dim)
             table = None          # the fused decode kernel takes the raw projections
-        if self.score_slopes is not None or self.v_head_dim != self.head_dim or self.exact_weights:
-            table = None          # ... and has no bias on its scores, one head size, bfloat16 weights
+        if self.score_slopes is not None or self.v_head_dim != self.head_dim or self.exact_weights or self.segment:
+            table = None          # ... and has no bias on its scores, one head size, bfloat16 weights, no segments
         if (table is not None and cache.writes and ctx.all_single and self.dtype == torch.bfloat16 and group <= 16
                 and self.head_dim in kernels.TC_HEAD_DIMS and self.head_dim % 32 == 0):
             # decode: rotary encoding, cache write and attention in one kernel
@@ -181,7 +241,7 @@ class PagedAttention:
         attn = torch.empty((n, self.o_dim), dtype=self.dtype, device=q.device)
         kernels.attention(attn, q, cache.k, cache.v, ctx, cache.block_table, self.n_heads, self.n_kv,
                           self.head_dim, self.window or 0, self.scale, score_slopes=self.score_slopes,
-                          v_head_dim=self.v_head_dim, exact_weights=self.exact_weights)
+                          v_head_dim=self.v_head_dim, exact_weights=self.exact_weights, segment=self.segment)
         return attn
 
     def forward(self, xn, ctx, cache):

@@ -14,7 +14,22 @@ its output, H rows of R values, goes through W_uv,h per head and then W_o.  The 
 values per token, [pages, 1, page_size, R], and the attention kernels read it as keys and as
 values (``PagedKVNeed.values_are_keys``).
 
-params: ``hidden``, ``n_heads``, ``head_dim`` (dk), ``v_head_dim`` (dv), ``q_rank`` (Rq),
+A second form, chosen by ``rot_dim`` > 0, adds positions and drops the query latent:
+
+    q_h = W_q,h h = [q_h plain (dk) | q_h rotated (dr)]            straight from the input
+    W_dkv h = [b (R) | k_rot (dr)];  c = rmsnorm(b) * g_kv;  k_rot is rotated, one part for all heads
+    score_h(j) = scale * (q_h plain . W_uk,h c_j + rot(q_h rotated) . rot(k_rot_j))
+    out = W_o ([a_1 v .. a_H v] * sigmoid(W_g h))                   with ``gate``
+
+The cached row is [c | rot(k_rot)], R + dr values, key of all heads; its first R values are also the
+value (``PagedKVNeed(values_are_keys, v_head_dim=R)``).  The query that meets it is
+[W_uk,h^T q_h plain | rot(q_h rotated)].  The rotation (``rotary``: {theta, scaling}, see
+``rotary.rotary_frequencies``) acts on all dr values, pair (i, i + dr / 2); angles are formed in double
+precision on the device, cos and sin carry the scaling's amplitude.  W_q, W_dkv and W_g are one stacked
+product whose float32 result feeds one kernel (csrc/latent.cu: latent norm, both rotations, cache write).
+
+params: ``hidden``, ``n_heads``, ``head_dim`` (dk), ``v_head_dim`` (dv), ``q_rank`` (Rq; None or 0 in
+the second form), ``rot_dim`` (dr, 0: the first form), ``rotary``, ``gate``, ``q`` / ``g`` among ``tensors``,
 ``kv_rank`` (R), ``scale``, ``eps`` (of both latent norms), ``window`` (None: every earlier
 key; W: the last W keys, the query's own included), ``cache_window`` (what the cache must
 keep: the widest window of all layers that read this cache; None: everything), ``sinks`` (True:
@@ -29,7 +44,7 @@ import torch
 from .. import kernels
 from .spec import BuildEnv, PagedKVNeed, PartSpec, TensorSpec, register_part
 
-_NAMES = ("dq", "dq_norm", "uq", "dkv", "dkv_norm", "uk", "uv", "sink", "o")
+_NAMES = ("dq", "dq_norm", "uq", "dkv", "dkv_norm", "uk", "uv", "sink", "o", "q", "g")
 
 
 class LatentAttention:
@@ -37,7 +52,19 @@ class LatentAttention:
         p = spec.params
         self.hidden = int(p["hidden"])
         self.H, self.dk, self.dv = int(p["n_heads"]), int(p["head_dim"]), int(p["v_head_dim"])
-        self.Rq, self.R = int(p["q_rank"]), int(p["kv_rank"])
+        self.Rq, self.R = int(p.get("q_rank") or 0), int(p["kv_rank"])
+        self.dr = int(p.get("rot_dim") or 0)
+        self.gate = bool(p.get("gate", False))
+        if (self.dr > 0) == (self.Rq > 0):
+            raise ValueError("latent attention: either a query latent (q_rank) or rotated parts (rot_dim)")
+        if (self.dr == 0 and self.gate) or self.dr % 2:
+            raise ValueError("latent attention: the gate belongs to the rotated form; rot_dim must be even")
+        self.freq, self.amplitude = None, 1.0
+        if self.dr:
+            from .rotary import rotary_frequencies
+            rot = p["rotary"]
+            freq, self.amplitude = rotary_frequencies(self.dr, float(rot["theta"]), rot.get("scaling"))
+            self.freq = freq.to(env.device)
         self.scale = float(p["scale"])
         self.eps = float(p["eps"])
         self.window = p.get("window")
@@ -52,6 +79,18 @@ class LatentAttention:
 
     def tensor_specs(self):
         n, d, H = self.names, self.hidden, self.H
+        if self.dr:
+            out = [TensorSpec(n["q"], (H * (self.dk + self.dr), d)),
+                   TensorSpec(n["dkv"], (self.R + self.dr, d)),
+                   TensorSpec(n["dkv_norm"], (self.R,), store="float32", init="gain"),
+                   TensorSpec(n["uk"], (H * self.dk, self.R)),
+                   TensorSpec(n["uv"], (H * self.dv, self.R)),
+                   TensorSpec(n["o"], (d, H * self.dv))]
+            if self.gate:
+                out.append(TensorSpec(n["g"], (H * self.dv, d)))
+            if self.has_sinks:
+                out.append(TensorSpec(n["sink"], (H,), store="float32", init="zeros"))
+            return out
         out = [TensorSpec(n["dq"], (self.Rq, d)),
                TensorSpec(n["dq_norm"], (self.Rq,), store="float32", init="gain"),
                TensorSpec(n["uq"], (H * self.dk, self.Rq)),
@@ -67,23 +106,53 @@ class LatentAttention:
 
     def bind(self, tensors):
         n = self.names
+        self.w_uk = tensors[n["uk"]].view(self.H, self.dk, self.R)      # head h: [dk, R], q_h^T times it
+        self.w_uv = tensors[n["uv"]].view(self.H, self.dv, self.R)      # head h: [dv, R]
+        self.w_o = tensors[n["o"]]
+        self.sink = tensors[n["sink"]].contiguous() if self.has_sinks else None
+        if self.dr:
+            # queries, latent with the rotated key part, gate: one product
+            rows = [tensors[n["q"]], tensors[n["dkv"]]] + ([tensors[n["g"]]] if self.gate else [])
+            self.w_in = torch.cat(rows, dim=0).contiguous()
+            self.g_kv = tensors[n["dkv_norm"]]
+            return
         self.w_dq = tensors[n["dq"]]
         # both down-projections are one product
         self.w_down = torch.cat([tensors[n["dq"]], tensors[n["dkv"]]], dim=0).contiguous() if self.own_latent else self.w_dq
         self.g_q = tensors[n["dq_norm"]]
         self.g_kv = tensors[n["dkv_norm"]] if self.own_latent else None
         self.w_uq = tensors[n["uq"]]
-        self.w_uk = tensors[n["uk"]].view(self.H, self.dk, self.R)      # head h: [dk, R], q_h^T times it
-        self.w_uv = tensors[n["uv"]].view(self.H, self.dv, self.R)      # head h: [dv, R]
-        self.w_o = tensors[n["o"]]
-        self.sink = tensors[n["sink"]].contiguous() if self.has_sinks else None
 
     def cache_need(self):
         if not self.own_latent:
             return None
+        if self.dr:
+            return PagedKVNeed(1, self.R + self.dr, self.cache_window, self.R, values_are_keys=True)
         return PagedKVNeed(1, self.R, self.cache_window, None, values_are_keys=True)
 
+    def _forward_rotated(self, xn, ctx, cache):
+        n, H, R, dr = xn.shape[0], self.H, self.R, self.dr
+        writes = cache.writes and self.own_latent
+        proj = kernels.linear(xn, self.w_in, out_dtype=torch.float32, small_ok=True)
+        q_plain = torch.empty((n, H * self.dk), dtype=self.dtype, device=xn.device)
+        q_full = torch.empty((n, H * (R + dr)), dtype=self.dtype, device=xn.device)
+        kernels.latent_rope_append(q_plain, q_full, proj, self.g_kv if writes else None, self.eps, self.freq,
+                                   self.amplitude, ctx.positions, ctx.token_req, cache.block_table if writes else None,
+                                   cache.k if writes else None, H, self.dk, dr, R)
+        # the plain query parts into the latent space, into the head of every head's row
+        kernels.linear_per_head(q_plain, self.w_uk, transposed=True, out=q_full.view(n, H, R + dr)[:, :, :R])
+        o_lat = torch.empty((n, H * R), dtype=self.dtype, device=xn.device)
+        kernels.attention(o_lat, q_full, cache.k, cache.k, ctx, cache.block_table, H, 1, R + dr, self.window or 0,
+                          self.scale, v_head_dim=R, sinks=self.sink, exact_weights=True)
+        o = kernels.linear_per_head(o_lat, self.w_uv)                                    # [n, H * dv]
+        if self.gate:
+            off = H * (self.dk + dr) + R + dr
+            kernels.sigmoid_gate(o, o, proj[:, off:off + H * self.dv])
+        return kernels.linear(o, self.w_o, out_dtype=torch.float32, small_ok=True)
+
     def forward(self, xn, ctx, cache):
+        if self.dr:
+            return self._forward_rotated(xn, ctx, cache)
         n = xn.shape[0]
         writes = cache.writes and self.own_latent
         proj = kernels.linear(xn, self.w_down if writes else self.w_dq, out_dtype=torch.float32, small_ok=True)

@@ -14,6 +14,9 @@ The router table stays float32 in both dtypes.  At bind time the experts' matric
 stacked into [E, 2f, d] (gate rows, then up rows) and [E, d, f].
 
 Further options, all absent by default:
+``groups`` {``count``, ``keep``}: the experts form ``count`` equal groups of neighbours, a group scores as
+its best expert, and only experts of the ``keep`` best groups can be chosen (the scores stay those over
+all experts).
 ``routing`` "table": no router; an integer table ``table_tensor`` [vocab, top] gives every token
 id its experts (the entries of a row differ), each with the weight ``table_weight`` (default
 1 / top), applied where ``weight_on`` says.  The ids are the step's own (``ctx.token_ids``;
@@ -69,6 +72,12 @@ class RoutedExperts:
         self.table_vocab = int(p.get("vocab") or 0)
         if self.routing == "table" and self.table_vocab <= 0:
             raise ValueError("routed experts: a routing table needs the vocabulary's size ('vocab')")
+        grp = p.get("groups") or {}
+        self.groups, self.groups_keep = int(grp.get("count") or 1), int(grp.get("keep") or 1)
+        if self.groups > 1 and (self.experts % self.groups or not (1 <= self.groups_keep <= self.groups)
+                                or self.top > self.groups_keep * (self.experts // self.groups)):
+            raise ValueError(f"routed experts: {self.top} of {self.experts} experts in {self.groups} groups of which "
+                             f"{self.groups_keep} are kept")
         self.act = self._activation(p)
         # a step with at least this many rows per expert on average, a table and ids that the host knows runs
         # the library's products expert by expert (``_forward_planned``); below it the grouped kernels
@@ -190,7 +199,8 @@ class RoutedExperts:
         if self.routing == "table":
             idx, wt = kernels.moe_table_route(ctx.token_ids, self.table, self.experts, self.table_weight, ctx.last_token)
         else:
-            idx, wt = kernels.moe_route(xn, self.router, self.top, self.score, self.renormalize)
+            idx, wt = kernels.moe_route(xn, self.router, self.top, self.score, self.renormalize, self.groups,
+                                        self.groups_keep)
         offsets, perm = kernels.moe_sort(idx, self.experts)
         on_input = self.weight_on == "input"
         act = kernels.moe_gemm(xn, self.w_gate_up, offsets, perm, wt, self.top, gated=True, scale_in=on_input, **self.act)

@@ -1,4 +1,4 @@
-"""RMSNorm with the residual sum folded in.
+"""RMSNorm with the residual sum folded in, and layer norm with gain and bias (``LayerNorm``, at the end).
 
 params: ``width``, ``eps``, optional ``tensor`` (the gain's full name where it is not
 ``<prefix>.weight``).  Tensor: ``<prefix>.weight`` [width], kept in float32
@@ -56,4 +56,34 @@ class RMSNorm:
         return out
 
 
+class LayerNorm:
+    """Layer norm with gain and bias: (x - mean) / sqrt(var + eps) * w + b, the variance being the
+    mean of the squared deviations.  params: ``width``, ``eps``, optional ``tensor`` (the gain's
+    full name where it is not ``<prefix>.weight``) and ``bias_tensor`` (default: the gain's name
+    + ``.b``).  Both tensors stay float32; mean, variance and scale are float32 in both dtypes.
+    Same interface as ``RMSNorm.forward``; no part folds this norm into its own kernels."""
+
+    def __init__(self, spec: PartSpec, env: BuildEnv):
+        self.width = int(spec.params["width"])
+        self.eps = float(spec.params["eps"])
+        self.name = spec.params.get("tensor") or spec.prefix + ".weight"
+        self.bias_name = spec.params.get("bias_tensor") or self.name + ".b"
+        self.dtype = env.dtype
+        self.gain = self.bias = None
+
+    def tensor_specs(self):
+        return [TensorSpec(self.name, (self.width,), store="float32", init="gain"),
+                TensorSpec(self.bias_name, (self.width,), store="float32", init="zeros")]
+
+    def bind(self, tensors):
+        self.gain, self.bias = tensors[self.name], tensors[self.bias_name]
+
+    def forward(self, x, res=None, rows=None):
+        n = x.shape[0] if rows is None else rows.numel()
+        out = torch.empty((n, self.width), dtype=self.dtype, device=x.device)
+        kernels.add_layernorm(x, res, out, self.gain, self.bias, self.eps, rows=rows)
+        return out
+
+
 register_part("norm", "rmsnorm", RMSNorm)
+register_part("norm", "layernorm", LayerNorm)

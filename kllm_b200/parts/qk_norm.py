@@ -50,4 +50,51 @@ class WholeProjectionNorm:
         return q
 
 
+class HeadNormRotary:
+    """``head_rmsnorm_rotary``: every query and key head is divided by its root mean square over its
+    ``head_dim`` values and multiplied by a gain [head_dim] that all heads share (``q_gain`` /
+    ``k_gain``: full tensor names, float32; None: no norm on that side), then the first ``rotary_dim``
+    values of every head are rotated (pair (i, i + rotary_dim / 2), angle position * f_i; ``theta``,
+    ``scaling`` as in ``rotary.rotary_frequencies``), before which the projections' biases are added
+    (the attention's ``bias``).  It offers ``prepare``: it takes the float32 result of the stacked
+    projection, so biases, sums, scales and the rotation are float32 and the angle is formed in double
+    precision on the device (no table, no bound on the position); it returns the queries in the model
+    dtype and writes keys and values, which may have fewer heads than the keys, into the layer's pages:
+    one kernel (csrc/qk_headnorm.cu)."""
+
+    def __init__(self, spec: PartSpec, env: BuildEnv):
+        from .rotary import rotary_frequencies
+        p = spec.params
+        self.head_dim = int(p["head_dim"])
+        self.eps = float(p.get("eps") or 0.0)
+        self.q_name, self.k_name = p.get("q_gain"), p.get("k_gain")
+        self.rot = int(p.get("rotary_dim") or 0)
+        if self.rot % 2 or self.rot > self.head_dim:
+            raise ValueError(f"rotary_dim {self.rot} must be even and within head_dim {self.head_dim}")
+        self.freq, self.amplitude = None, 1.0
+        if self.rot:
+            freq, self.amplitude = rotary_frequencies(self.rot, float(p["theta"]), p.get("scaling"))
+            self.freq = freq.to(env.device)
+        self.dtype = env.dtype
+        self.q_gain = self.k_gain = None
+
+    def tensor_specs(self):
+        return [TensorSpec(n, (self.head_dim,), store="float32", init="gain") for n in (self.q_name, self.k_name) if n]
+
+    def bind(self, tensors):
+        self.q_gain = tensors[self.q_name] if self.q_name else None
+        self.k_gain = tensors[self.k_name] if self.k_name else None
+
+    def prepare(self, qkv, ctx, cache, attn):
+        q_heads, k_heads = attn.n_heads * attn.maps, attn.n_kv * attn.maps
+        q = torch.empty((qkv.shape[0], q_heads * self.head_dim), dtype=self.dtype, device=qkv.device)
+        writes = cache.writes
+        kernels.headnorm_rope_append(q, qkv, attn.bias, self.q_gain, self.k_gain, self.eps, self.freq, self.amplitude,
+                                     self.rot, ctx.positions, ctx.token_req, cache.block_table if writes else None,
+                                     cache.k if writes else None, cache.v if writes else None, q_heads, k_heads,
+                                     attn.n_kv, self.head_dim, attn.v_head_dim)
+        return q
+
+
 register_part("qk_transform", "whole_rmsnorm", WholeProjectionNorm)
+register_part("qk_transform", "head_rmsnorm_rotary", HeadNormRotary)

@@ -95,21 +95,35 @@ class PagedKVNeed:
     v_head_dim: the size of a head's values where it differs from the keys' (None: the same).
     values_are_keys: one row per token serves as key and as value (a layer that attends
     through a cached low-rank latent): no value store is kept, the views of the values are the
-    keys'."""
+    keys'; with a ``v_head_dim`` below ``head_dim`` the values are the first ``v_head_dim`` elements
+    of that row (a row that carries something beside the latent for the keys alone).
+    n_v_heads: the heads of the value store where they are fewer than the key heads (None: the
+    same): n_kv_heads / n_v_heads neighbouring key heads attend over one value head."""
     n_kv_heads: int
     head_dim: int
     window: Optional[int] = None
     v_head_dim: Optional[int] = None
     values_are_keys: bool = False
+    n_v_heads: Optional[int] = None
 
     @property
     def value_dim(self) -> int:
         return self.v_head_dim or self.head_dim
 
     @property
+    def value_heads(self) -> int:
+        return self.n_v_heads or self.n_kv_heads
+
+    @property
     def stored_dim(self) -> int:
-        """Elements kept per token and kv head."""
+        """Elements kept per token and kv head (with the same number of key and value heads)."""
         return self.head_dim if self.values_are_keys else self.head_dim + self.value_dim
+
+    @property
+    def stored_per_token(self) -> int:
+        """Elements kept per token over all heads."""
+        keys = self.n_kv_heads * self.head_dim
+        return keys if self.values_are_keys else keys + self.value_heads * self.value_dim
 
 
 @dataclass(frozen=True)
