@@ -44,6 +44,8 @@ own kernels one by one against their rooflines beside the Llama kernel that does
 work.  A record of its own; the default line does not change.
 ``--design nutizen`` does the same for the Nutizen design (attention over cached low-rank
 latents in a window with sinks, several residual streams, experts assigned by a table).
+``--design ronurax`` does the same for the Ronurax design (two-map attention in mask segments,
+attention through a latent with a rotated key part, layer norms, experts chosen within groups).
 """
 from __future__ import annotations
 
@@ -250,8 +252,8 @@ def main():
     ap.add_argument("--workload", default="", choices=["", "llama2-7b-mixed"],
                     help="llama2-7b-mixed: 32 requests, prompts uniform in [128, 3072], 128 new tokens each, through "
                          "the scheduler (a record of its own, not the bench line)")
-    ap.add_argument("--design", default="", choices=["", "sozarax", "nutizen"],
-                    help="sozarax, nutizen: prefill and decode of that design at two layer sizes beside a Llama of equal size, and "
+    ap.add_argument("--design", default="", choices=["", "sozarax", "nutizen", "ronurax"],
+                    help="sozarax, nutizen, ronurax: prefill and decode of that design at two layer sizes beside a Llama of equal size, and "
                          "its kernels against their rooflines (a record of its own, not the bench line)")
     args = ap.parse_args()
     if args.timeline:
@@ -648,6 +650,31 @@ def nutizen_config(width, layers, heads, head_dim, ff, experts, top, expert_ff, 
             "streams": streams, "layers": out}
 
 
+def ronurax_config(width, layers, heads, kv_heads, head_dim, experts, top, expert_ff, vocab, kv_rank, rot_dim, segment,
+                   groups, keep):
+    """A Ronurax model of ``layers`` layers, two-map attention and latent attention in turn, experts in every
+    layer.  The two-map layers have half the heads with two maps each and values twice as wide, so that
+    their projections are as large as those of ``heads`` plain heads of ``head_dim``."""
+    att = {"heads": heads // 2, "kv_heads": max(1, kv_heads // 2), "dim": head_dim, "vdim": 2 * head_dim,
+           "scale": head_dim ** -0.5, "diff": 0.8, "mask": {"size": segment},
+           "rot": {"base": 500000.0, "dims": head_dim, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}}
+    lat = {"heads": heads, "dim": head_dim, "rot_dim": rot_dim, "vdim": head_dim, "kv_rank": kv_rank,
+           "scale": (head_dim + rot_dim) ** -0.5,
+           "rot": {"base": 10000.0, "dims": rot_dim, "scaling": {"factor": 40.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}
+    moe = {"kind": "moe", "expert": {"ff": expert_ff},
+           "router": {"experts": experts, "top": top, "groups": {"count": groups, "keep": keep}}}
+    return {"architecture": "Ronurax", "vocab": vocab, "width": width, "norm": {"eps": 1e-6},
+            "layers": [{"type": "attention" if i % 2 == 0 else "latent_attention", "mixer": dict(att if i % 2 == 0 else lat),
+                        "mlp": dict(moe)} for i in range(layers)]}
+
+
+RONURAX_EXTRA = {
+    # name: key/value latent, rotated size, mask segment, experts chosen, groups, groups kept
+    "2048-wide": (128, 32, 1024, 4, 4, 2),
+    "4096-wide": (192, 64, 1024, 4, 4, 2),
+}
+
+
 NUTIZEN_EXTRA = {
     # name: query latent, key/value latent, window, residual streams
     "2048-wide": (768, 128, 1024, 4),
@@ -993,8 +1020,223 @@ def design_comparison(args):
             del wsets, dsets
         return rows
 
+    def ronurax_rows(width, heads, kv, hd, ff, E, eff, R, dr, segment, top, groups, keep):
+        """The Ronurax design's own kernels, each beside the Llama kernel that does the like work."""
+        rows = []
+        dev, f32 = "cuda", torch.float32
+        hbm, tens = pk["hbm_gbs"] * 1e9, pk["bf16_tflops"] * 1e12
+        esz = 2 if dtype == "bfloat16" else 4
+        tc = dtype == "bfloat16"
+
+        def note(name, us, bytes_=0, flops=0, like=None):
+            t_mem, t_flop = bytes_ / hbm * 1e6, flops / tens * 1e6
+            floor = max(t_mem, t_flop)
+            rows.append({"kernel": name, "us": round(us, 1), "floor_us": round(floor, 2),
+                         "bound": "memory" if t_mem >= t_flop else "tensor",
+                         "times_floor": round(us / floor, 1) if floor > 0 else None, "like": like})
+
+        def ctx_of(n_new, start):
+            import itertools
+            import types
+            Sq = len(n_new)
+            qs = torch.tensor([0] + list(itertools.accumulate(n_new)), dtype=torch.int32, device=dev)
+            return types.SimpleNamespace(
+                n_tokens=sum(n_new), n_requests=Sq, q_start=qs,
+                token_req=torch.repeat_interleave(torch.arange(Sq, dtype=torch.int32), torch.tensor(n_new)).to(dev),
+                start_pos=torch.tensor(start, dtype=torch.int32, device=dev),
+                positions=torch.cat([torch.arange(s, s + c, dtype=torch.int32) for s, c in zip(start, n_new)]).to(dev),
+                host_n_new=list(n_new), host_start_pos=list(start), all_single=all(c == 1 for c in n_new),
+                max_ctx=max(s + c for s, c in zip(start, n_new)), split_bound=0, max_new=max(n_new))
+
+        Hd, Gd, dv = heads // 2, max(1, kv // 2), 2 * hd          # the two-map layer: heads, key/value heads, value size
+        Dk = R + dr
+        for name, n_new, start in (("attention prefill", [T], [0]), ("attention decode", [1] * B, [ctx - 1] * B)):
+            c = ctx_of(n_new, start)
+            n, Sq = sum(n_new), len(n_new)
+            per = -(-max(s + m for s, m in zip(start, n_new)) // page)
+            table = torch.arange(Sq * per, dtype=torch.int32, device=dev).view(Sq, per).contiguous()
+            it = [0]
+            # ---- two maps per head in mask segments, and their combination ----
+            pairs = sum(p % segment + 1 for s, m in zip(start, n_new) for p in range(s, s + m))
+            seen = sum((s + m) - ((s // segment) * segment) for s, m in zip(start, n_new))
+            stores = rotate(lambda: (torch.randn(Sq * per, 2 * Gd, page, hd, device=dev).to(tdt),
+                                     torch.randn(Sq * per, Gd, page, dv, device=dev).to(tdt)),
+                            Sq * per * page * (2 * Gd * hd + Gd * dv) * esz)
+            q = (torch.randn(n, 2 * Hd * hd, device=dev) * 0.2).to(tdt)
+            both = torch.empty(n, 2 * Hd * dv, device=dev)
+            out = torch.empty(n, Hd * dv, dtype=tdt, device=dev)
+
+            def call():
+                i = it[0] = it[0] + 1
+                kc, vc = stores[i % len(stores)]
+                kernels.attention(both, q, kc, vc, c, table, 2 * Hd, 2 * Gd, hd, 0, hd ** -0.5, v_head_dim=dv,
+                                  exact_weights=True, segment=segment)
+                kernels.maps_combine(out, both, Gd, Hd // Gd, dv, 0.4, 1e-6, 0.2)
+            us = timed(call, inner=4) * 1e3
+            note("two-map " + name, us, seen * (2 * Gd * hd + Gd * dv) * esz + n * (2 * Hd * hd + Hd * dv) * esz,
+                 pairs * 2 * Hd * (2.0 * hd + 2.0 * dv) if tc else 0, like="llama " + name)
+            del stores
+            # ---- H heads over one cached row [latent | rotated key part] per key, causal ----
+            pairs_c = sum(p + 1 for s, m in zip(start, n_new) for p in range(s, s + m))
+            seen_c = sum(s + m for s, m in zip(start, n_new))
+            rows_ = rotate(lambda: torch.randn(Sq * per, 1, page, Dk, device=dev).to(tdt), Sq * per * page * Dk * esz)
+            q2 = (torch.randn(n, heads * Dk, device=dev) * 0.1).to(tdt)
+            whole = kernels.tensor_core_rows(Dk, heads, tdt)
+            o2 = torch.empty(n, heads * (Dk if whole else R), dtype=tdt, device=dev)
+
+            def call2():
+                i = it[0] = it[0] + 1
+                st = rows_[i % len(rows_)]
+                kernels.attention(o2, q2, st, st, c, table, heads, 1, Dk, 0, (hd + dr) ** -0.5,
+                                  v_head_dim=None if whole else R, exact_weights=True)
+            us = timed(call2, inner=4) * 1e3
+            note("latent+rotated " + name, us, seen_c * Dk * esz + n * heads * (Dk + R) * esz,
+                 pairs_c * heads * (2.0 * Dk + 2.0 * R) if tc else 0, like="llama " + name)
+            del rows_
+            # ---- Llama's attention: in windows as long as the segments, and causal ----
+            caches = rotate(lambda: (torch.randn(Sq * per, kv, page, hd, device=dev).to(tdt),
+                                     torch.randn(Sq * per, kv, page, hd, device=dev).to(tdt)), 2 * Sq * per * kv * page * hd * esz)
+            q3 = (torch.randn(n, heads * hd, device=dev) * 0.2).to(tdt)
+            o3 = torch.empty_like(q3)
+            for label, win in (("llama " + name + f", window {segment}", segment), ("llama " + name, 0)):
+                def call3():
+                    i = it[0] = it[0] + 1
+                    kc, vc = caches[i % len(caches)]
+                    kernels.attention(o3, q3, kc, vc, c, table, heads, kv, hd, win, hd ** -0.5)
+                us = timed(call3, inner=4) * 1e3
+                pw = sum(min(p + 1, win or (1 << 30)) for s, m in zip(start, n_new) for p in range(s, s + m))
+                sw = sum(min(s + m, (win + m - 1) if win else (1 << 30)) for s, m in zip(start, n_new))
+                note(label, us, sw * kv * hd * 2 * esz + 2 * n * heads * hd * esz, 4.0 * pw * heads * hd if tc else 0)
+            del caches
+        # ---- what lies between the projections and the attention: biases, head norms, rotation, cache write ----
+        for name, n_new, start in (("prefill", [T], [0]), ("decode", [1] * B, [ctx - 1] * B)):
+            c = ctx_of(n_new, start)
+            n, Sq = sum(n_new), len(n_new)
+            per = -(-max(s + m for s, m in zip(start, n_new)) // page)
+            table = torch.arange(Sq * per, dtype=torch.int32, device=dev).view(Sq, per).contiguous()
+            wq = (2 * Hd + 2 * Gd) * hd + Gd * dv
+            qkvs = rotate(lambda: torch.randn(n, wq, device=dev), n * wq * 4)
+            kc = torch.zeros(Sq * per, 2 * Gd, page, hd, dtype=tdt, device=dev)
+            vc = torch.zeros(Sq * per, Gd, page, dv, dtype=tdt, device=dev)
+            bias, gain = torch.zeros(wq, device=dev), torch.ones(hd, device=dev)
+            freq = torch.pow(torch.tensor(500000.0, dtype=torch.float64), -torch.arange(hd // 2, dtype=torch.float64) * 2 / hd).to(dev)
+            qo = torch.empty(n, 2 * Hd * hd, dtype=tdt, device=dev)
+            it = [0]
+
+            def prep():
+                i = it[0] = it[0] + 1
+                kernels.headnorm_rope_append(qo, qkvs[i % len(qkvs)], bias, gain, gain, 1e-6, freq, 1.0, hd, c.positions,
+                                             c.token_req, table, kc, vc, 2 * Hd, 2 * Gd, Gd, hd, dv)
+            us = timed(prep, inner=4) * 1e3
+            note(f"bias + head norm + rotation + cache write {name}", us, n * wq * (4 + esz), like=f"llama rotation + cache write {name}")
+            wl = heads * (hd + dr) + R + dr
+            projs = rotate(lambda: torch.randn(n, wl, device=dev), n * wl * 4)
+            store = torch.zeros(Sq * per, 1, page, Dk, dtype=tdt, device=dev)
+            gk = torch.ones(R, device=dev)
+            fr = torch.pow(torch.tensor(10000.0, dtype=torch.float64), -torch.arange(dr // 2, dtype=torch.float64) * 2 / dr).to(dev)
+            qp = torch.empty(n, heads * hd, dtype=tdt, device=dev)
+            qf = torch.empty(n, heads * Dk, dtype=tdt, device=dev)
+
+            def prep2():
+                i = it[0] = it[0] + 1
+                kernels.latent_rope_append(qp, qf, projs[i % len(projs)], gk, 1e-6, fr, 1.3, c.positions, c.token_req, table,
+                                           store, heads, hd, dr, R)
+            us = timed(prep2, inner=4) * 1e3
+            note(f"latent norm + rotations + cache write {name}", us, n * wl * (4 + esz), like=f"llama rotation + cache write {name}")
+            wk = (heads + 2 * kv) * hd
+            qs = rotate(lambda: (torch.randn(n, wk, device=dev)).to(tdt), n * wk * esz)
+            kc2 = torch.zeros(Sq * per, kv, page, hd, dtype=tdt, device=dev)
+            vc2 = torch.zeros_like(kc2)
+            pos_t = torch.arange(max(ctx, T), dtype=torch.float64)[:, None] * torch.pow(
+                torch.tensor(10000.0, dtype=torch.float64), -torch.arange(hd // 2, dtype=torch.float64) * 2 / hd)[None, :]
+            table_cs = torch.cat([torch.cos(pos_t), torch.sin(pos_t)], dim=1).float().to(dev).contiguous()
+
+            def prep3():
+                i = it[0] = it[0] + 1
+                x = qs[i % len(qs)]
+                kernels.rope_append(x[:, :heads * hd], x[:, heads * hd:(heads + kv) * hd], x[:, (heads + kv) * hd:], table_cs,
+                                    c.positions, c.token_req, table, kc2, vc2, heads, kv, hd)
+            us = timed(prep3, inner=4) * 1e3
+            note(f"llama rotation + cache write {name}", us, n * wk * 2 * esz)
+            del qkvs, projs, qs
+        # ---- the residual sum with a layer norm (gain and bias) beside Llama's with an RMS norm ----
+        for name, n in (("prefill", T), ("decode", B)):
+            xs = rotate(lambda: torch.randn(n, width, device=dev), n * width * 4)
+            y = torch.randn(n, width, device=dev)
+            gain, bias = torch.ones(width, device=dev), torch.zeros(width, device=dev)
+            normed = torch.empty(n, width, dtype=tdt, device=dev)
+            it = [0]
+
+            def ln():
+                i = it[0] = it[0] + 1
+                kernels.add_layernorm(xs[i % len(xs)], y, normed, gain, bias, 1e-6)
+            us = timed(ln, inner=4) * 1e3
+            note(f"sum + layer norm {name}", us, 3 * n * width * 4 + n * width * esz, like=f"llama sum+norm {name}")
+
+            def rn():
+                i = it[0] = it[0] + 1
+                kernels.add_rmsnorm(xs[i % len(xs)], y, normed, gain, 1e-6)
+            us = timed(rn, inner=4) * 1e3
+            note(f"llama sum+norm {name}", us, 3 * n * width * 4 + n * width * esz)
+            del xs
+        # ---- experts chosen within the best groups, their scores on the outputs; Llama's dense products ----
+        for name, n in (("prefill", T), ("decode", B)):
+            x = (torch.randn(n, width, device=dev) * 0.5).to(tdt)
+            router = torch.randn(E, width, device=dev) * 0.05
+            wsets = rotate(lambda: ((torch.randn(E, 2 * eff, width, device=dev) * 0.02).to(tdt),
+                                    (torch.randn(E, width, eff, device=dev) * 0.02).to(tdt)), 3 * E * eff * width * esz)
+            it = [0]
+
+            def experts():
+                i = it[0] = it[0] + 1
+                gu, dn = wsets[i % len(wsets)]
+                idx, wt = kernels.moe_route(x, router, top, score="softmax", renormalize=False, groups=groups, keep=keep)
+                offsets, perm = kernels.moe_sort(idx, E)
+                act = kernels.moe_gemm(x, gu, offsets, perm, wt, top, gated=True)
+                kernels.moe_combine(kernels.moe_gemm(act, dn, offsets, perm, wt, top, gated=False, scale_out=True), top)
+            us = timed(experts, inner=2) * 1e3
+            used = min(E, n * top)
+            note(f"experts within groups ({top} of {E}, {keep} of {groups} groups) {name}", us, 3.0 * used * eff * width * esz,
+                 6.0 * n * top * eff * width if tc else 0, like=f"llama gate/up/down {name}")
+            dsets = rotate(lambda: ((torch.randn(2 * ff, width, device=dev) * 0.02).to(tdt),
+                                    (torch.randn(width, ff, device=dev) * 0.02).to(tdt)), 3 * ff * width * esz)
+            resid = torch.zeros(n, width, device=dev)
+
+            def dense():
+                i = it[0] = it[0] + 1
+                gu, dn = dsets[i % len(dsets)]
+                if n <= 16 and dtype == "bfloat16":
+                    act = kernels.skinny_gemm(gu[:ff], weight_up=gu[ff:], x=x, epilogue="swiglu")
+                    kernels.skinny_gemm(dn, x=act, epilogue="add", out=resid)
+                else:
+                    yy = kernels.linear(x, gu, out_dtype=f32)
+                    act = torch.empty(n, ff, dtype=tdt, device=dev)
+                    kernels.silu_mul(act, yy[:, :ff], yy[:, ff:])
+                    kernels.linear_add(resid, act, dn)
+            us = timed(dense, inner=2) * 1e3
+            note(f"llama gate/up/down {name}", us, 3.0 * ff * width * esz, 6.0 * n * ff * width if tc else 0)
+            del wsets, dsets
+        return rows
+
     sizes = {}
     for name, (width, layers, heads, kv, hd, ff, E, top, eff, vocab) in DESIGN_SIZES.items():
+        if args.design == "ronurax":
+            R, dr, segment, rtop, groups, keep = RONURAX_EXTRA[name]
+            ron = ronurax_config(width, layers, heads, kv, hd, E, rtop, eff, vocab, R, dr, segment, groups, keep)
+            llama = dict(TINYLLAMA, num_hidden_layers=layers, hidden_size=width, num_attention_heads=heads,
+                         num_key_value_heads=kv, head_dim=hd, intermediate_size=ff, vocab_size=vocab,
+                         max_position_embeddings=max(ctx, T))
+            print(f"[bench] {name}: Ronurax", file=sys.stderr, flush=True)
+            rec = {"layers": layers, "two_map_heads": f"{heads // 2} x 2 maps of {hd}, values {2 * hd}, {max(1, kv // 2)} kv heads",
+                   "latent_heads": f"{heads} of {hd} + {dr} rotated, latent {R}", "segment": segment, "ff": ff,
+                   "experts": f"{rtop} of {E} x {eff}, {keep} of {groups} groups", "ronurax": model_run(ron, vocab)}
+            print(f"[bench] {name}: Llama of equal size", file=sys.stderr, flush=True)
+            rec["llama"] = model_run(llama, vocab)
+            print(f"[bench] {name}: kernels", file=sys.stderr, flush=True)
+            rec["kernels"] = ronurax_rows(width, heads, kv, hd, ff, E, eff, R, dr, segment, rtop, groups, keep)
+            sizes[name] = rec
+            torch.cuda.empty_cache()
+            continue
         if args.design == "nutizen":
             Rq, R, window, S = NUTIZEN_EXTRA[name]
             nut = nutizen_config(width, layers, heads, hd, ff, E, top, eff, vocab, Rq, R, window, S)

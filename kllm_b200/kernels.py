@@ -547,6 +547,12 @@ USE_TCGEN05 = os.environ.get("KLLM_B200_TCGEN05", "1") != "0"
 _sm_count = {}
 
 
+def tensor_core_rows(head_dim: int, group: int, dtype: torch.dtype) -> bool:
+    """Whether ``attention`` runs bfloat16 rows of this size, with ``group`` heads on a kv head and values as
+    wide as keys, on the ``mma.sync`` kernels (also with ``exact_weights`` or sinks)."""
+    return dtype == torch.bfloat16 and (head_dim in TC_HEAD_DIMS or head_dim in TC_WIDE_HEAD_DIMS) and group <= 64
+
+
 def sm_count() -> int:
     """Streaming multiprocessors of the current device (148 on a B200)."""
     dev = torch.cuda.current_device()
@@ -1171,27 +1177,32 @@ def linear_per_head(x: torch.Tensor, weight: torch.Tensor, transposed: bool = Fa
     [H, b, a] (``transposed``: weight [H, a, b], used as weight[h]^T), y [n, H * b] in x's dtype.
     One batched product of the vendor GEMM library over the heads, reading x and writing y in
     place at their head strides (bfloat16 operands accumulate in float32; float32 operands
-    run as true float32)."""
+    run as true float32).  x may also be a view [n, H, a] with dense rows of a wider tensor (the
+    head of every head's row)."""
     _cuda(x, weight)
     if torch.backends.cuda.matmul.allow_tf32:
         raise KernelError("TF32 matmul mode is on; the float32 path must stay true 32-bit")
     n, H = x.shape[0], weight.shape[0]
     a = weight.shape[1] if transposed else weight.shape[2]
     b = weight.shape[2] if transposed else weight.shape[1]
-    if x.dtype != weight.dtype or not x.is_contiguous() or x.shape[1] != H * a:
+    if x.dim() == 3:
+        if x.dtype != weight.dtype or tuple(x.shape) != (n, H, a) or x.stride(2) != 1:
+            raise KernelError("linear_per_head: a view x must be [n, heads, a] with dense rows, in the weights' dtype")
+    elif x.dtype != weight.dtype or not x.is_contiguous() or x.shape[1] != H * a:
         raise KernelError("linear_per_head: x must be contiguous [n, heads * a] in the weights' dtype")
+    x = x if x.dim() == 3 else x.view(n, H, a)
     if out is not None:
         # the heads' results into a view [n, H, b] of a wider row (rows dense in b)
         if tuple(out.shape) != (n, H, b) or out.dtype != x.dtype or out.stride(2) != 1:
             raise KernelError("linear_per_head: out must be a view [n, heads, b] in x's dtype with dense rows")
         y3 = out.transpose(0, 1)
         if out.stride(0) % 8 == 0 and out.stride(1) % 8 == 0 and out.data_ptr() % 16 == 0:
-            torch.bmm(x.view(n, H, a).transpose(0, 1), weight if transposed else weight.transpose(1, 2), out=y3)
+            torch.bmm(x.transpose(0, 1), weight if transposed else weight.transpose(1, 2), out=y3)
         else:
-            y3.copy_(torch.bmm(x.view(n, H, a).transpose(0, 1), weight if transposed else weight.transpose(1, 2)))
+            y3.copy_(torch.bmm(x.transpose(0, 1), weight if transposed else weight.transpose(1, 2)))
         return out
     y = torch.empty((n, H * b), dtype=x.dtype, device=x.device)
-    torch.bmm(x.view(n, H, a).transpose(0, 1), weight if transposed else weight.transpose(1, 2),
+    torch.bmm(x.transpose(0, 1), weight if transposed else weight.transpose(1, 2),
               out=y.view(n, H, b).transpose(0, 1))
     return y
 

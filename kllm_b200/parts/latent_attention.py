@@ -22,7 +22,9 @@ A second form, chosen by ``rot_dim`` > 0, adds positions and drops the query lat
     out = W_o ([a_1 v .. a_H v] * sigmoid(W_g h))                   with ``gate``
 
 The cached row is [c | rot(k_rot)], R + dr values, key of all heads; its first R values are also the
-value (``PagedKVNeed(values_are_keys, v_head_dim=R)``).  The query that meets it is
+value (``PagedKVNeed(values_are_keys, v_head_dim=R)``; in bfloat16 with R + dr a head size of the
+tensor-core kernels the whole row runs as the value and the last dr columns of every head's result are
+not read).  The query that meets it is
 [W_uk,h^T q_h plain | rot(q_h rotated)].  The rotation (``rotary``: {theta, scaling}, see
 ``rotary.rotary_frequencies``) acts on all dr values, pair (i, i + dr / 2); angles are formed in double
 precision on the device, cos and sin carry the scaling's amplitude.  W_q, W_dkv and W_g are one stacked
@@ -76,6 +78,8 @@ class LatentAttention:
         names = dict(p.get("tensors") or {})
         self.names = {k: names.get(k) or f"{spec.prefix}.{k}" for k in _NAMES}
         self.dtype = env.dtype
+        # bfloat16 rows of a size the tensor-core attention is built for: the whole cached row serves as value
+        self.whole_rows = bool(self.dr) and kernels.tensor_core_rows(self.R + self.dr, self.H, self.dtype)
 
     def tensor_specs(self):
         n, d, H = self.names, self.hidden, self.H
@@ -141,10 +145,18 @@ class LatentAttention:
                                    cache.k if writes else None, H, self.dk, dr, R)
         # the plain query parts into the latent space, into the head of every head's row
         kernels.linear_per_head(q_plain, self.w_uk, transposed=True, out=q_full.view(n, H, R + dr)[:, :, :R])
-        o_lat = torch.empty((n, H * R), dtype=self.dtype, device=xn.device)
-        kernels.attention(o_lat, q_full, cache.k, cache.k, ctx, cache.block_table, H, 1, R + dr, self.window or 0,
-                          self.scale, v_head_dim=R, sinks=self.sink, exact_weights=True)
-        o = kernels.linear_per_head(o_lat, self.w_uv)                                    # [n, H * dv]
+        if self.whole_rows:
+            # the tensor-core kernels take values as wide as keys: the whole row is the value, and the
+            # dr columns that the rotated key part adds to every head's result are left unread
+            o_lat = torch.empty((n, H * (R + dr)), dtype=self.dtype, device=xn.device)
+            kernels.attention(o_lat, q_full, cache.k, cache.k, ctx, cache.block_table, H, 1, R + dr, self.window or 0,
+                              self.scale, sinks=self.sink, exact_weights=True)
+            o = kernels.linear_per_head(o_lat.view(n, H, R + dr)[:, :, :R], self.w_uv)   # [n, H * dv]
+        else:
+            o_lat = torch.empty((n, H * R), dtype=self.dtype, device=xn.device)
+            kernels.attention(o_lat, q_full, cache.k, cache.k, ctx, cache.block_table, H, 1, R + dr, self.window or 0,
+                              self.scale, v_head_dim=R, sinks=self.sink, exact_weights=True)
+            o = kernels.linear_per_head(o_lat, self.w_uv)                                # [n, H * dv]
         if self.gate:
             off = H * (self.dk + dr) + R + dr
             kernels.sigmoid_gate(o, o, proj[:, off:off + H * self.dv])

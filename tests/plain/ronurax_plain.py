@@ -114,6 +114,23 @@ def segment_mask(T, size):
 
 # ---- mixers -----------------------------------------------------------------------------
 
+def two_map_heads(q, k, v, visible, scale, lam, diff, eps):
+    """q [T, H, 2, dk], k [T, G, 2, dk], v [T, G, dv] -> [T, H, dv]: every head has two softmax maps over
+    the same values; o = a1 - lam a2, divided by its root mean square over dv, times (1 - diff)."""
+    T, H = q.shape[:2]
+    G, dv = v.shape[1], v.shape[2]
+    out = np.zeros((T, H, dv))
+    for hh in range(H):
+        g = hh // (H // G)
+        a = [softmax_rows(q[:, hh, mp] @ k[:, g, mp].T * scale, visible) @ v[:, g] for mp in (0, 1)]
+        out[:, hh] = rms_norm(a[0] - lam * a[1], None, eps) * (1.0 - diff)
+    return out
+
+
+def map_lambda(lq1, lk1, lq2, lk2, diff):
+    return math.exp(float(np.sum(f64(lq1) * f64(lk1)))) - math.exp(float(np.sum(f64(lq2) * f64(lk2)))) + diff
+
+
 def differential_attention(h, w, p, m, eps):
     """Two softmax maps per head over the same values, combined as a1 - lambda a2."""
     H, G, dk, dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
@@ -132,15 +149,20 @@ def differential_attention(h, w, p, m, eps):
         k = rotate(k, pos, freq, rot["dims"])
     vis = segment_mask(T, m["mask"]["size"]) if m.get("mask") else causal_mask(T)
     diff = float(m["diff"])
-    lam = (math.exp(float(np.sum(f64(w[p + "lq1"]) * f64(w[p + "lk1"]))))
-           - math.exp(float(np.sum(f64(w[p + "lq2"]) * f64(w[p + "lk2"])))) + diff)
-    out = np.zeros((T, H, dv))
-    for hh in range(H):
-        g = hh // (H // G)
-        a = [softmax_rows(q[:, hh, mp] @ k[:, g, mp].T * float(m["scale"]), vis) @ v[:, g] for mp in (0, 1)]
-        o = a[0] - lam * a[1]
-        out[:, hh] = rms_norm(o, None, eps) * (1.0 - diff)
+    lam = map_lambda(w[p + "lq1"], w[p + "lk1"], w[p + "lq2"], w[p + "lk2"], diff)
+    out = two_map_heads(q, k, v, vis, float(m["scale"]), lam, diff, eps)
     return out.reshape(T, H * dv) @ f64(w[p + "o"]).T
+
+
+def latent_heads(q_plain, q_rot, k_plain, k_rot, v, visible, scale):
+    """q_plain [T, H, dk], q_rot [T, H, dr] (rotated), k_plain [T, H, dk], k_rot [T, dr] (rotated, one for
+    all heads), v [T, H, dv] -> [T, H, dv]."""
+    T, H = q_plain.shape[:2]
+    out = np.zeros((T, H, v.shape[2]))
+    for hh in range(H):
+        s = (q_plain[:, hh] @ k_plain[:, hh].T + q_rot[:, hh] @ k_rot.T) * scale
+        out[:, hh] = softmax_rows(s, visible) @ v[:, hh]
+    return out
 
 
 def latent_attention(h, w, p, m, eps):
@@ -152,19 +174,14 @@ def latent_attention(h, w, p, m, eps):
     q = (h @ f64(w[p + "q"]).T).reshape(T, H, dk + dr)
     down = h @ f64(w[p + "dkv"]).T
     c = rms_norm(down[:, :R], w[p + "dkv.norm"], eps)
-    k_rot = down[:, R:]
     k_plain = (c @ f64(w[p + "uk"]).T).reshape(T, H, dk)
     v = (c @ f64(w[p + "uv"]).T).reshape(T, H, dv)
     rot = m["rot"]
     freq, amp = stretched_by_ramp(base_frequencies(dr, float(rot["base"])), dr, float(rot["base"]), rot.get("scaling"))
     pos = np.arange(T)
     q_rot = rotate(q[:, :, dk:], pos, freq, dr, amp)
-    k_rot = rotate(k_rot, pos, freq, dr, amp)
-    vis = causal_mask(T)
-    out = np.zeros((T, H, dv))
-    for hh in range(H):
-        s = (q[:, hh, :dk] @ k_plain[:, hh].T + q_rot[:, hh] @ k_rot.T) * float(m["scale"])
-        out[:, hh] = softmax_rows(s, vis) @ v[:, hh]
+    k_rot = rotate(down[:, R:], pos, freq, dr, amp)
+    out = latent_heads(q[:, :, :dk], q_rot, k_plain, k_rot, v, causal_mask(T), float(m["scale"]))
     gate = sigmoid(h @ f64(w[p + "g"]).T)
     return (out.reshape(T, H * dv) * gate) @ f64(w[p + "o"]).T
 
@@ -228,3 +245,78 @@ def forward(w, cfg, ids, taps=None):
             taps.append(x.copy())
     xn = layer_norm(x, w["final.norm"], w["final.norm.b"], eps)
     return xn @ f64(w["head"]).T
+
+
+# ---- random models for the tests --------------------------------------------------------
+
+def round_bf16(a):
+    """Round float values to the nearest bfloat16 (ties to even), returned as float64."""
+    a = np.ascontiguousarray(a, dtype=np.float32)
+    bits = a.view(np.uint32).astype(np.uint64)
+    bits = (bits + 0x7FFF + ((bits >> 16) & 1)) & 0xFFFF0000
+    return bits.astype(np.uint32).view(np.float32).astype(np.float64).reshape(a.shape)
+
+
+def tensor_shapes(cfg):
+    """name -> (shape, kind) of every tensor of a configuration."""
+    d, out = cfg["width"], {}
+    out["embed"] = ((cfg["vocab"], d), "matrix")
+    for i, L in enumerate(cfg["layers"]):
+        if "weights_of" in L:
+            continue
+        p, m = f"l{i}.", L["mixer"]
+        for nm in ("norm1",) + (("norm2",) if L.get("mlp") else ()):
+            out[p + nm] = ((d,), "gain")
+            out[p + nm + ".b"] = ((d,), "bias")
+        if L["type"] == "attention":
+            H, G, dk, dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+            out[p + "mix.q"] = ((H * 2 * dk, d), "qk")
+            out[p + "mix.k"] = ((G * 2 * dk, d), "qk")
+            out[p + "mix.v"] = ((G * dv, d), "matrix")
+            out[p + "mix.q.b"], out[p + "mix.k.b"], out[p + "mix.v.b"] = ((H * 2 * dk,), "bias"), ((G * 2 * dk,), "bias"), \
+                ((G * dv,), "bias")
+            out[p + "mix.q.norm"], out[p + "mix.k.norm"] = ((dk,), "gain"), ((dk,), "gain")
+            for nm in ("lq1", "lk1", "lq2", "lk2"):
+                out[p + "mix." + nm] = ((dk,), "lambda")
+            out[p + "mix.o"] = ((d, H * dv), "matrix")
+        else:
+            H, dk, dr, dv, R = m["heads"], m["dim"], m["rot_dim"], m["vdim"], m["kv_rank"]
+            out[p + "mix.q"] = ((H * (dk + dr), d), "qk")
+            out[p + "mix.dkv"] = ((R + dr, d), "qk")
+            out[p + "mix.dkv.norm"] = ((R,), "gain")
+            out[p + "mix.uk"] = ((H * dk, R), "matrix")
+            out[p + "mix.uv"] = ((H * dv, R), "matrix")
+            out[p + "mix.g"] = ((H * dv, d), "matrix")
+            out[p + "mix.o"] = ((d, H * dv), "matrix")
+        if L.get("mlp"):
+            f, E = L["mlp"]["expert"]["ff"], L["mlp"]["router"]["experts"]
+            out[p + "mlp.router"] = ((E, d), "router")
+            for e in range(E):
+                out[f"{p}mlp.e{e}.gate"], out[f"{p}mlp.e{e}.up"] = ((f, d), "matrix"), ((f, d), "matrix")
+                out[f"{p}mlp.e{e}.down"] = ((d, f), "matrix")
+    out["final.norm"], out["final.norm.b"] = ((d,), "gain"), ((d,), "bias")
+    out["head"] = ((cfg["vocab"], d), "matrix")
+    return out
+
+
+def random_weights(cfg, seed, std=0.08, qk_boost=2.0):
+    """Random tensors, all exactly representable in bfloat16.  Query and key projections are
+    scaled up so that attention is far from uniform; router rows are spread so that choices are
+    not close calls."""
+    rng = np.random.default_rng(seed)
+    w = {}
+    for name, (shape, kind) in tensor_shapes(cfg).items():
+        if kind == "matrix":
+            a = rng.normal(0.0, std, size=shape)
+        elif kind == "qk":
+            a = rng.normal(0.0, std * qk_boost, size=shape)
+        elif kind == "router":
+            a = rng.normal(0.0, 0.5, size=shape)
+        elif kind == "gain":
+            a = 1.0 + rng.normal(0.0, 0.1, size=shape)
+        elif kind == "bias":
+            a = rng.normal(0.0, 0.1, size=shape)
+        elif kind == "lambda":
+            a = rng.normal(0.0, 0.15, size=shape)
+        w[name] = round_bf16(a.astype(np.float32))
+    return w
