@@ -43,6 +43,11 @@
 #ifndef KLLM_HD
 #error "compile with -DKLLM_HD=<head size>"
 #endif
+// Values of another size than the keys: -DKLLM_VD=<value size>.  Such a library holds the prefill
+// kernel alone (the decode kernels are built for values as wide as the keys).
+#ifndef KLLM_VD
+#define KLLM_VD KLLM_HD
+#endif
 
 KLLM_EXPORT_LAST_ERROR(attention_tc)
 
@@ -51,12 +56,16 @@ namespace {
 constexpr int HD = KLLM_HD;
 static_assert(HD % 16 == 0 && HD >= 16 && HD <= 256, "head size must be a multiple of 16 up to 256");
 constexpr int KSTEPS = HD / 16;          // MMA k-steps over the head dims (scores)
-constexpr int DTILES = HD / 8;           // 8-wide output tiles over the head dims
+constexpr int VD = KLLM_VD;              // size of a head's values and of its output
+static_assert(VD % 16 == 0 && VD >= 16 && VD <= 256, "value size must be a multiple of 16 up to 256");
+constexpr int DTILES = VD / 8;           // 8-wide output tiles over the value dims
+constexpr int VCHUNKS = VD / 8;          // 16-byte pieces of a value row
+constexpr int ROWV = VD + 8;             // padded value row, in elements
 constexpr int CHUNKS = HD / 8;           // 16-byte pieces of a key row
 constexpr int TILE = 64;                 // keys per shared-memory tile
 constexpr int ROW = HD + 8;              // padded row, in elements (16 bytes of padding)
 constexpr int THREADS = 128;
-constexpr int STAGE_ELEMS = 2 * TILE * ROW;                       // K tile then V tile
+constexpr int STAGE_ELEMS = TILE * (ROW + ROWV);                  // K tile then V tile
 // Decode CTAs are few and each walks a short key range: the deeper the pipeline,
 // the more of the range is in flight at once (with 5 stages a range of 256 keys is
 // requested whole before the first tile is used).  Prefill keeps 3 stages and more
@@ -135,6 +144,42 @@ __device__ __forceinline__ void load_tile(bf16* stage, const bf16* __restrict__ 
     }
 }
 
+// The same for a value store of its own shape: `v_heads` heads (kv head g reads value head gv),
+// `v_row` elements from one value row to the next, of which the first VD are the values.
+__device__ __forceinline__ void load_tile_wide(bf16* stage, const bf16* __restrict__ kcache,
+                                               const bf16* __restrict__ vcache, const int* table,
+                                               int key0, int hi, int g, int n_kv, int gv, int v_heads, int v_row,
+                                               int page_size) {
+    bf16* sk = stage;
+    bf16* sv = stage + TILE * ROW;
+    for (int c = threadIdx.x; c < TILE * CHUNKS; c += THREADS) {
+        const int row = c / CHUNKS, ch = c - row * CHUNKS;
+        const int key = key0 + row;
+        const bool valid = key < hi;
+        int64_t off = 0;
+        if (valid) {
+            const int lp = key / page_size;
+            off = (((int64_t)table[lp] * n_kv + g) * page_size + (key - lp * page_size)) * HD + ch * 8;
+        }
+        cp_async16(sk + row * ROW + ch * 8, kcache + off, valid);
+    }
+    for (int c = threadIdx.x; c < TILE * VCHUNKS; c += THREADS) {
+        const int row = c / VCHUNKS, ch = c - row * VCHUNKS;
+        const int key = key0 + row;
+        const bool valid = key < hi;
+        int64_t off = 0;
+        if (valid) {
+            const int lp = key / page_size;
+            off = (((int64_t)table[lp] * v_heads + gv) * page_size + (key - lp * page_size)) * v_row + ch * 8;
+        }
+        cp_async16(sv + row * ROWV + ch * 8, vcache + off, valid);
+    }
+}
+
+// what rounding to bfloat16 leaves of x
+__device__ __forceinline__ float bf16_rest(float x) { return x - __bfloat162float(__float2bfloat16_rn(x)); }
+
+#if KLLM_VD == KLLM_HD
 // Scores of 16 rows against keys [16*slice, 16*slice+16) of a K tile.
 __device__ __forceinline__ void scores16(float (&s)[2][4], const uint32_t (&qa)[KSTEPS][4], const bf16* sk,
                                          int slice, int lane) {
@@ -199,9 +244,6 @@ struct DecodeFusion {
     // n_kv / share, everything else goes by group.
     int share;
 };
-
-// what rounding to bfloat16 leaves of x
-__device__ __forceinline__ float bf16_rest(float x) { return x - __bfloat162float(__float2bfloat16_rn(x)); }
 
 // Merge of the splits of one (token, kv head) by one CTA.  (m, l) of row r and split j
 // sit at ml + r * ml_r + j * ml_j, the partial output row at po + r * o_r + j * o_j, in
@@ -562,21 +604,26 @@ __global__ void attn_combine_kernel(bf16* __restrict__ out, const float* __restr
     }
 }
 
+#endif  // KLLM_VD == KLLM_HD
+
 // ---- prefill ------------------------------------------------------------------
 
 // Rows per warp in the prefill kernel: two 16-row MMA tiles share every key and value
 // fragment (half the shared-memory reads per flop) where the registers allow it.
-constexpr int MT = HD <= 64 ? 2 : 1;
+constexpr int MT = (HD <= 64 && VD <= 64) ? 2 : 1;
 constexpr int PRE_ROWS = 4 * 16 * MT;          // rows (token x head of the group) per CTA
 
+// `segment` C > 0: positions are cut into segments of C counted from 0 of the sequence and a row sees
+// only the keys of its own token's segment.  `v_heads`, `v_row`: shape of the value store (see
+// load_tile_wide).  `out_f32`: the output rows are float32 instead of bfloat16.
 __global__ void __launch_bounds__(THREADS)
-attn_prefill_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, int64_t q_stride,
+attn_prefill_kernel(void* __restrict__ out_, const bf16* __restrict__ q, int64_t q_stride,
                     const bf16* __restrict__ kcache, const bf16* __restrict__ vcache,
                     const int* __restrict__ q_start, const int* __restrict__ start_pos,
                     const int* __restrict__ block_table, int max_blocks, int n_requests, int n_heads,
                     int n_kv, int page_size, int window, float scale_log2e, int tokens_per_tile,
                     const float* __restrict__ slopes, float inv_scale, int split_p,
-                    const float* __restrict__ sinks) {
+                    const float* __restrict__ sinks, int segment, int v_heads, int v_row, int out_f32) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     bf16* smem = reinterpret_cast<bf16*>(smem_raw);
     __shared__ int s_req, s_tok0;
@@ -605,8 +652,11 @@ attn_prefill_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, int64_t 
     const int q_end = q_start[req + 1];
     const int n_tok = min(tokens_per_tile, q_end - tok0);
     const int pos0 = start_pos[req] + (tok0 - q_start[req]);      // position of the tile's first token
-    const int lo = (window > 0 && pos0 + 1 > window) ? pos0 + 1 - window : 0;
     const int hi = pos0 + n_tok;                                   // last token's position + 1
+    int lo = (window > 0 && pos0 + 1 > window) ? pos0 + 1 - window : 0;
+    if (segment > 0) lo = max(lo, pos0 - pos0 % segment);          // the first token's segment starts the range
+    const bool plain_v = VD == HD && v_heads == n_kv && v_row == HD;
+    const int gv = g / (n_kv / v_heads);
     const int* table = block_table + (int64_t)req * max_blocks;
     const int ntiles = (hi - lo + TILE - 1) / TILE;
 
@@ -627,10 +677,11 @@ attn_prefill_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, int64_t 
             vr[m][h] = tt < n_tok;
             pr[m][h] = vr[m][h] ? pos0 + tt : -1;
             wr[m][h] = (window > 0) ? pr[m][h] + 1 - window : 0;
+            if (segment > 0 && vr[m][h]) wr[m][h] = max(wr[m][h], pr[m][h] - pr[m][h] % segment);
             sl_[m][h] = (slopes && vr[m][h]) ? slopes[g * gs + hh] * inv_scale : 0.f;
             sk_[m][h] = (sinks && vr[m][h]) ? sinks[g * gs + hh] * inv_scale : -INFINITY;
             qp[h] = q + (int64_t)(tok0 + tt) * q_stride + (int64_t)(g * gs + hh) * HD;
-            orow[m][h] = (int64_t)(tok0 + tt) * n_heads * HD + (int64_t)(g * gs + hh) * HD;
+            orow[m][h] = (int64_t)(tok0 + tt) * n_heads * VD + (int64_t)(g * gs + hh) * VD;
         }
 #pragma unroll
         for (int ks = 0; ks < KSTEPS; ks++) {
@@ -647,6 +698,16 @@ attn_prefill_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, int64_t 
     const bool warp_active = wt_first < n_tok;
     const int warp_hi = pos0 + wt_last + 1;
     const int warp_full_below = pos0 + wt_first;                    // keys <= this are causal for every row
+    // first key that the warp's first (last) token sees: tiles wholly below the one are skipped, tiles that
+    // begin below the other need the mask
+    int warp_lo = 0, warp_lo_last = 0;
+    if (warp_active) {
+        if (window > 0) { warp_lo = max(0, pos0 + wt_first + 1 - window); warp_lo_last = max(0, pos0 + wt_last + 1 - window); }
+        if (segment > 0) {
+            warp_lo = max(warp_lo, (pos0 + wt_first) - (pos0 + wt_first) % segment);
+            warp_lo_last = max(warp_lo_last, (pos0 + wt_last) - (pos0 + wt_last) % segment);
+        }
+    }
 
     float o[MT][DTILES][4];
     float mx[MT][2], l[MT][2];
@@ -665,7 +726,10 @@ attn_prefill_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, int64_t 
 
 #pragma unroll
     for (int s = 0; s < PRE_STAGES - 1; s++) {
-        if (s < ntiles) load_tile(smem + s * STAGE_ELEMS, kcache, vcache, table, lo + s * TILE, hi, g, n_kv, page_size);
+        if (s < ntiles) {
+            if (plain_v) load_tile(smem + s * STAGE_ELEMS, kcache, vcache, table, lo + s * TILE, hi, g, n_kv, page_size);
+            else load_tile_wide(smem + s * STAGE_ELEMS, kcache, vcache, table, lo + s * TILE, hi, g, n_kv, gv, v_heads, v_row, page_size);
+        }
         cp_async_commit();
     }
     const int mi = lane >> 3;
@@ -673,14 +737,17 @@ attn_prefill_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, int64_t 
         cp_async_wait<PRE_STAGES - 2>();
         __syncthreads();
         const int nxt = i + PRE_STAGES - 1;
-        if (nxt < ntiles)
-            load_tile(smem + (nxt % PRE_STAGES) * STAGE_ELEMS, kcache, vcache, table, lo + nxt * TILE, hi, g, n_kv, page_size);
+        if (nxt < ntiles) {
+            bf16* stage = smem + (nxt % PRE_STAGES) * STAGE_ELEMS;
+            if (plain_v) load_tile(stage, kcache, vcache, table, lo + nxt * TILE, hi, g, n_kv, page_size);
+            else load_tile_wide(stage, kcache, vcache, table, lo + nxt * TILE, hi, g, n_kv, gv, v_heads, v_row, page_size);
+        }
         cp_async_commit();
         const bf16* sk = smem + (i % PRE_STAGES) * STAGE_ELEMS;
         const bf16* sv = sk + TILE * ROW;
         const int key0 = lo + i * TILE;
-        if (!warp_active || key0 >= warp_hi) continue;             // nothing of this tile is visible to the warp
-        const bool need_mask = window > 0 || key0 + TILE - 1 > warp_full_below;
+        if (!warp_active || key0 >= warp_hi || key0 + TILE <= warp_lo) continue;   // nothing of this tile is visible to the warp
+        const bool need_mask = key0 < warp_lo_last || key0 + TILE - 1 > warp_full_below;
         // scores of the warp's rows against the 64 keys: every key fragment serves all MT tiles
         float s[MT][8][4];
 #pragma unroll
@@ -768,7 +835,7 @@ attn_prefill_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, int64_t 
         // output += P . V: every value fragment serves all MT tiles
 #pragma unroll
         for (int sl = 0; sl < 4; sl++) {
-            const bf16* base = sv + (16 * sl + (mi & 1) * 8 + (lane & 7)) * ROW + (mi >> 1) * 8;
+            const bf16* base = sv + (16 * sl + (mi & 1) * 8 + (lane & 7)) * ROWV + (mi >> 1) * 8;
             uint32_t pl[MT][4];          // what the rounding of this slice's probabilities left
             if (split_p) {
 #pragma unroll
@@ -780,7 +847,7 @@ attn_prefill_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, int64_t 
                 }
             }
 #pragma unroll
-            for (int dp = 0; dp < HD / 16; dp++) {
+            for (int dp = 0; dp < VD / 16; dp++) {
                 uint32_t v[4];
                 ldmatrix_x4_trans(v, base + dp * 16);
 #pragma unroll
@@ -805,7 +872,15 @@ attn_prefill_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, int64_t 
             lv += __shfl_xor_sync(0xffffffffu, lv, 2);
             if (!vr[m][h]) continue;
             const float inv = 1.f / lv;
-            bf16* op = out + orow[m][h];
+            if (out_f32) {
+                float* op = reinterpret_cast<float*>(out_) + orow[m][h];
+#pragma unroll
+                for (int dt = 0; dt < DTILES; dt++)
+                    *reinterpret_cast<float2*>(op + dt * 8 + 2 * tq) =
+                        make_float2(o[m][dt][2 * h] * inv, o[m][dt][2 * h + 1] * inv);
+                continue;
+            }
+            bf16* op = reinterpret_cast<bf16*>(out_) + orow[m][h];
 #pragma unroll
             for (int dt = 0; dt < DTILES; dt++)
                 *reinterpret_cast<uint32_t*>(op + dt * 8 + 2 * tq) =
@@ -822,10 +897,12 @@ int set_attributes() {
     auto raise = [&](auto kernel, int bytes) {
         if (e == cudaSuccess) e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
     };
+#if KLLM_VD == KLLM_HD
     raise(attn_decode_kernel<false, DEC_STAGES_DEEP>, dec_smem_bytes(DEC_STAGES_DEEP));
     raise(attn_decode_kernel<true, DEC_STAGES_DEEP>, dec_smem_bytes(DEC_STAGES_DEEP));
     raise(attn_decode_kernel<false, DEC_STAGES_WIDE>, dec_smem_bytes(DEC_STAGES_WIDE));
     raise(attn_decode_kernel<true, DEC_STAGES_WIDE>, dec_smem_bytes(DEC_STAGES_WIDE));
+#endif
     raise(attn_prefill_kernel, PRE_SMEM_BYTES);
     if (e != cudaSuccess) {
         snprintf(g_kllm_err, sizeof(g_kllm_err), "attention: cannot get %d bytes of shared memory: %s", dec_smem_bytes(DEC_STAGES_DEEP),
@@ -847,6 +924,9 @@ int check_common(int n_heads, int n_kv, int hd, int page_size, const void* q, in
 }  // namespace
 
 extern "C" int kllm_attention_tc_head_dim() { return HD; }
+extern "C" int kllm_attention_tc_value_dim() { return VD; }
+
+#if KLLM_VD == KLLM_HD
 
 // Decode form: every token on its own (any batch is valid, one token per request
 // is what it is made for).  part_o [n_tokens, n_heads, num_splits, HD] float32 and
@@ -994,16 +1074,25 @@ extern "C" int kllm_attention_decode_static(void* out, const void* q, int64_t q_
                                  num_splits, nullptr, 0, nullptr, stream);
 }
 
+#endif  // KLLM_VD == KLLM_HD
+
 // Prefill form: requests' portions q_start[s]..q_start[s+1] (prefix sums, [n_requests+1])
-// starting at cache position start_pos[s].
+// starting at cache position start_pos[s].  `vd`: the value size this library was built for;
+// `segment`, `v_heads`, `v_row`, `out_f32` as the kernel describes them.
 extern "C" int kllm_attention_prefill(void* out, const void* q, int64_t q_stride, const void* kcache,
                                       const void* vcache, const int* q_start, const int* start_pos,
                                       const int* block_table, int max_blocks, int n_tokens, int n_requests,
                                       int n_heads, int n_kv, int hd, int page_size, int window, float scale,
-                                      const float* slopes, int split_p, const float* sinks, void* stream) {
+                                      const float* slopes, int split_p, const float* sinks, int vd, int segment,
+                                      int v_heads, int v_row, int out_f32, void* stream) {
     if (n_tokens <= 0) return 0;
     int rc = check_common(n_heads, n_kv, hd, page_size, q, q_stride);
     if (rc) return rc;
+    if (vd != VD) KLLM_FAIL("attention prefill: this library was built for value size %d, not %d", VD, vd);
+    if (v_heads <= 0 || n_kv % v_heads || v_row < VD || v_row % 8 || ((uintptr_t)vcache & 15) || ((uintptr_t)kcache & 15))
+        KLLM_FAIL("attention prefill: %d value heads under %d kv heads, value rows of %d elements", v_heads, n_kv, v_row);
+    if (segment < 0) KLLM_FAIL("attention prefill: segment %d", segment);
+    if (((uintptr_t)out & 7)) KLLM_FAIL("attention prefill: out must be 8-byte aligned");
     const int gs = n_heads / n_kv;
     if (gs > 64) KLLM_FAIL("attention prefill: %d heads per kv head, at most 64", gs);
     if ((slopes || sinks) && !(scale > 0.f)) KLLM_FAIL("attention prefill: a bias on the scores or a sink needs a positive scale");
@@ -1013,8 +1102,8 @@ extern "C" int kllm_attention_prefill(void* out, const void* q, int64_t q_stride
     const float sl2e = scale * 1.4426950408889634f;
     dim3 grid(max_tiles * n_kv);
     kllm_launch((attn_prefill_kernel), dim3(grid), dim3(THREADS), PRE_SMEM_BYTES, (cudaStream_t)stream, 
-        (bf16*)out, (const bf16*)q, q_stride, (const bf16*)kcache, (const bf16*)vcache, q_start, start_pos,
+        out, (const bf16*)q, q_stride, (const bf16*)kcache, (const bf16*)vcache, q_start, start_pos,
         block_table, max_blocks, n_requests, n_heads, n_kv, page_size, window, sl2e, tpt, slopes,
-        (slopes || sinks) ? 1.f / scale : 0.f, split_p, sinks);
+        (slopes || sinks) ? 1.f / scale : 0.f, split_p, sinks, segment, v_heads, v_row, out_f32);
     KLLM_LAUNCH_STATUS();
 }

@@ -455,7 +455,7 @@ SIMT_CHUNK = 256      # keys per CTA when a decoding token's context is cut (att
 def attention_simt(out: torch.Tensor, q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, ctx,
                    block_table: torch.Tensor, n_heads: int, n_kv: int, head_dim: int, window: int,
                    scale: float, score_slopes: Optional[torch.Tensor] = None, v_head_dim: Optional[int] = None,
-                   sinks: Optional[torch.Tensor] = None, segment: int = 0) -> None:
+                   sinks: Optional[torch.Tensor] = None, segment: int = 0, upto: Optional[int] = None) -> None:
     """Causal GQA attention of the step's tokens on the CUDA cores, float32 arithmetic
     (csrc/attention_simt.cu): the attention of the float32 path.  The requests that bring
     one token each at the head of the batch (decoding requests, which the scheduler puts
@@ -470,7 +470,9 @@ def attention_simt(out: torch.Tensor, q: torch.Tensor, kcache: torch.Tensor, vca
     The value store may have fewer heads than the key store (``vcache`` [pages, v_heads, page_size,
     row]: n_kv / v_heads neighbouring key heads read one value head) and rows longer than
     ``v_head_dim`` (the values are then the head of each row: a store whose rows are keys and, in
-    their first part, values).  ``out`` may be float32 beside bfloat16 operands."""
+    their first part, values).  ``out`` may be float32 beside bfloat16 operands.  ``upto``: only the
+    first ``upto`` requests are served, which bring one token each (the caller gives the portions
+    after them to another kernel)."""
     _cuda(out, q, kcache, vcache, block_table, score_slopes, sinks)
     _slopes_arg(sinks, n_heads, "sinks")
     vd = int(v_head_dim or head_dim)
@@ -488,9 +490,11 @@ def attention_simt(out: torch.Tensor, q: torch.Tensor, kcache: torch.Tensor, vca
         raise KernelError("attention: cache layout must be [pages, n_kv, page_size, head_dim]")
     group = n_heads // max(1, n_kv)
     lib = load_library("attention_simt")
-    n_req = ctx.n_requests
+    n_req, n_tokens = ctx.n_requests, ctx.n_tokens
     singles = n_req if ctx.all_single else 0
-    if not ctx.all_single and ctx.host_n_new:
+    if upto is not None:
+        n_req = n_tokens = singles = int(upto)
+    elif not ctx.all_single and ctx.host_n_new:
         while singles < n_req and ctx.host_n_new[singles] == 1:
             singles += 1
     bound = ctx.split_bound or ctx.max_ctx
@@ -518,7 +522,7 @@ def attention_simt(out: torch.Tensor, q: torch.Tensor, kcache: torch.Tensor, vca
         first = singles
     if first < n_req:
         qt = max(1, 64 // group)
-        rest = ctx.n_tokens - first
+        rest = n_tokens - first
         rc = lib.kllm_attention_simt(_p(out), None, None, _p(q), ctypes.c_int64(q.stride(0)), _p(kcache), _p(vcache),
                                      _p(ctx.q_start[first:]), _p(ctx.start_pos[first:]), _p(block_table[first:]),
                                      block_table.shape[1], n_req - first, rest // qt + (n_req - first), *common, qt, 0, 1,
@@ -597,13 +601,13 @@ def attention(out: torch.Tensor, q: torch.Tensor, kcache: torch.Tensor, vcache: 
     taken by the CUDA-core kernel and the ``mma.sync`` kernels, not by the tcgen05 kernels.
     ``exact_weights``: the softmax weights, computed in float32, must not meet the values
     rounded to one bfloat16: the ``mma.sync`` kernels then feed them to the tensor cores as
-    two bfloat16 terms (16 bits of mantissa), the CUDA-core kernel as float32.  Values of
-    another size than the keys (``v_head_dim``) are taken by the CUDA-core kernel alone.
+    two bfloat16 terms (16 bits of mantissa), the CUDA-core kernel as float32.
     ``sinks`` (float32 [n_heads]): exp(sinks[h]) joins the denominator of head h's softmax, a
     term without a key or a value; taken by the CUDA-core kernels and the ``mma.sync`` kernels.
-    ``segment`` (a query sees only the keys of its own segment of that many positions), a value
-    store with fewer heads than the key store or with rows that the values only head, and a
-    float32 ``out`` beside bfloat16 operands are taken by the CUDA-core kernels."""
+    ``segment`` (a query sees only the keys of its own segment of that many positions), values of
+    another size than the keys, a value store with fewer heads than the key store or with rows that
+    the values only head, and a float32 ``out`` beside bfloat16 operands are taken by the CUDA-core
+    kernels and, for portions in bfloat16 with sizes in steps of 16, by the ``mma.sync`` prefill kernel."""
     group = n_heads // max(1, n_kv)
     vd = int(v_head_dim or head_dim)
     special = score_slopes is not None or exact_weights
@@ -611,6 +615,28 @@ def attention(out: torch.Tensor, q: torch.Tensor, kcache: torch.Tensor, vcache: 
     plain_values = vcache.shape[1] == n_kv and vcache.shape[3] == vd and out.dtype == q.dtype
     tc = (q.dtype == torch.bfloat16 and (head_dim in TC_HEAD_DIMS or head_dim in TC_WIDE_HEAD_DIMS) and vd == head_dim
           and not (special and scale <= 0) and not segment and plain_values)
+    # what the plain tensor-core route refuses, the prefill kernel takes in its wide form (bfloat16 rows, sizes
+    # in steps of 16): portions go there, the single tokens at the head of the batch to the CUDA cores
+    wide = (not tc and q.dtype == torch.bfloat16 and (head_dim in TC_HEAD_DIMS or head_dim in TC_WIDE_HEAD_DIMS)
+            and vd % 16 == 0 and 16 <= vd <= 256 and group <= 64 and not (special and scale <= 0)
+            and vcache.dim() == 4 and vcache.shape[3] % 8 == 0 and not ctx.all_single and bool(ctx.host_n_new))
+    if wide:
+        singles = 0
+        while singles < ctx.n_requests and ctx.host_n_new[singles] == 1:
+            singles += 1
+        if singles:
+            if not simt_fits(q, n_heads, n_kv, head_dim, vd):
+                wide = False
+            else:
+                attention_simt(out, q, kcache, vcache, ctx, block_table, n_heads, n_kv, head_dim, window, scale,
+                               score_slopes, vd, sinks, segment, upto=singles)
+    if wide:
+        if singles < ctx.n_requests:
+            attention_prefill(out, q, kcache, vcache, ctx.q_start[singles:], ctx.start_pos[singles:],
+                              block_table[singles:], ctx.n_requests - singles, n_heads, n_kv, head_dim, window, scale,
+                              slopes=score_slopes, split_weights=exact_weights, sinks=sinks, v_head_dim=vd,
+                              segment=segment)
+        return
     if (special or vd != head_dim or segment or not plain_values) and not (tc and group <= 64):
         if not simt_fits(q, n_heads, n_kv, head_dim, vd) or vcache.shape[3] % 4:
             # head sizes that are no multiples of 4, very wide groups: one warp per (token, head)
@@ -733,19 +759,31 @@ def attention_decode_fused(out, q, k_new, v_new, cos_sin, kcache, vcache, positi
 
 def attention_prefill(out, q, kcache, vcache, q_start, start_pos, block_table, n_requests, n_heads, n_kv,
                       head_dim, window, scale, slopes: Optional[torch.Tensor] = None,
-                      split_weights: bool = False, sinks: Optional[torch.Tensor] = None) -> None:
+                      split_weights: bool = False, sinks: Optional[torch.Tensor] = None,
+                      v_head_dim: Optional[int] = None, segment: int = 0) -> None:
     """Tensor-core attention of portions: request s brings rows q_start[s]..q_start[s+1]
     that start at cache position start_pos[s].  ``slopes``, ``split_weights`` and ``sinks`` as in
-    ``attention_decode``."""
+    ``attention_decode``.  ``v_head_dim`` (values of another size than the keys: a library of its
+    own per pair of sizes), ``segment``, a value store of another shape than the key store and a
+    float32 ``out`` as in ``attention_simt``."""
     _cuda(out, q, kcache, vcache, q_start, start_pos, block_table, slopes, sinks)
-    _check_attention(out, q, kcache, vcache, block_table, n_kv, head_dim)
+    vd = int(v_head_dim or head_dim)
+    if q.dtype != torch.bfloat16 or out.dtype not in (torch.bfloat16, torch.float32) or kcache.dtype != torch.bfloat16:
+        raise KernelError("tensor-core attention takes bfloat16 operands (out bfloat16 or float32)")
+    if q.stride(1) != 1 or not out.is_contiguous() or not kcache.is_contiguous() or out.shape[1] != n_heads * vd:
+        raise KernelError("attention: out and caches contiguous, q rows dense")
+    if kcache.shape[1] != n_kv or kcache.shape[3] != head_dim:
+        raise KernelError("attention: cache layout must be [pages, n_kv, page_size, head_dim]")
+    v_heads, v_row = _value_layout(kcache, vcache, n_kv, vd)
+    _i32(block_table, "block_table")
     _i32(q_start, "q_start"); _i32(start_pos, "start_pos")
-    lib = load_library("attention_tc", {"KLLM_HD": head_dim})
+    lib = load_library("attention_tc", {"KLLM_HD": head_dim} if vd == head_dim else {"KLLM_HD": head_dim, "KLLM_VD": vd})
     rc = lib.kllm_attention_prefill(_p(out), _p(q), ctypes.c_int64(q.stride(0)), _p(kcache), _p(vcache),
                                     _p(q_start), _p(start_pos), _p(block_table), block_table.shape[1],
                                     q.shape[0], int(n_requests), n_heads, n_kv, head_dim, kcache.shape[2],
                                     int(window or 0), ctypes.c_float(scale), _slopes_arg(slopes, n_heads),
-                                    int(bool(split_weights)), _slopes_arg(sinks, n_heads, "sinks"), _stream())
+                                    int(bool(split_weights)), _slopes_arg(sinks, n_heads, "sinks"), vd,
+                                    int(segment or 0), v_heads, v_row, int(out.dtype == torch.float32), _stream())
     _check(lib, "attention_tc", rc)
 
 

@@ -411,6 +411,63 @@ def test_two_map_attention_at_segment_edges(dtype, H, G, dk, dv):
             assert np.abs(got - want[T - n_new:]).max() <= tol * np.abs(want).max(), (C, T, far, n_new)
 
 
+def _plain_rows(q, k, v, pos, first, scale):
+    """softmax(scale q . k) v of one row over the keys first .. pos, in double precision."""
+    sc = (k[first:pos + 1] @ q) * scale
+    w = np.exp(sc - sc.max())
+    return (w / w.sum()) @ v[first:pos + 1]
+
+
+@pytest.mark.parametrize("dk,dv,Hk,Hv,gs,row", [(64, 128, 4, 2, 2, 128), (32, 64, 2, 2, 3, 64), (128, 64, 2, 1, 1, 64),
+                                                (48, 16, 1, 1, 5, 48), (16, 32, 6, 3, 1, 40), (96, 96, 2, 1, 4, 96)])
+@pytest.mark.parametrize("segment,window", [(0, 0), (50, 0), (0, 33), (128, 70), (7, 0)])
+def test_mixed_step_with_values_of_another_size(dk, dv, Hk, Hv, gs, row, segment, window):
+    """One launch of single tokens and portions of unequal requests in bfloat16, keys of one size, values of
+    another in a store of fewer heads whose rows may be longer than the values, float32 results: every row
+    against the plain softmax over the keys that its segment and its window leave.  Portions begin and end
+    inside segments, windows and 64-key tiles; the pages are scattered and unused ones hold NaN."""
+    import torch
+    from kllm_b200 import kernels
+    rng = np.random.default_rng(dk * 7 + dv + segment + window)
+    page, n_pages, scale = 16, 96, 0.3
+    # (tokens of this step, tokens before): two single tokens first, then portions
+    reqs = [(1, 130), (1, 0), (70, 0), (3, 125), (129, 60), (1, 77), (2, 510), (64, 64)]
+    H = Hk * gs
+    free = list(rng.permutation(n_pages))
+    kc = np.full((n_pages, Hk, page, dk), np.nan)
+    vc = np.full((n_pages, Hv, page, row), np.nan)
+    table = np.full((len(reqs), 48), -1)
+    qs, want = [], []
+    for r, (n, before) in enumerate(reqs):
+        T = n + before
+        q = P.round_bf16(rng.standard_normal((T, H, dk)))
+        k = P.round_bf16(rng.standard_normal((T, Hk, dk)))
+        v = P.round_bf16(rng.standard_normal((T, Hv, row)))
+        ids = [free.pop() for _ in range(-(-T // page))]
+        table[r, :len(ids)] = ids
+        for t in range(T):
+            kc[ids[t // page], :, t % page] = k[t]
+            vc[ids[t // page], :, t % page] = v[t]
+        for t in range(before, T):
+            first = max(t - t % segment if segment else 0, t + 1 - window if window else 0)
+            want.append([_plain_rows(q[t, h], k[:, h // gs], v[:, (h // gs) // (Hk // Hv), :dv], t, first, scale)
+                         for h in range(H)])
+        qs.append(q[before:].reshape(n, H * dk))
+    want = np.asarray(want).reshape(-1, H * dv)
+    ctx = _ctx([n for n, _ in reqs], [b for _, b in reqs])
+    out = torch.full((ctx.n_tokens, H * dv), float("nan"), dtype=torch.float32, device="cuda")
+    kernels.attention(out, _t(np.concatenate(qs), "bfloat16"), _t(kc, "bfloat16"), _t(vc, "bfloat16"), ctx,
+                      _t(table, "int32"), H, Hk, dk, window, scale, v_head_dim=dv, exact_weights=True, segment=segment)
+    got = out.cpu().numpy()
+    assert np.isfinite(got).all()
+    bad = np.abs(got - want).max(axis=1)
+    assert bad.max() <= 1e-4 * np.abs(want).max(), (int(bad.argmax()), float(bad.max()))
+    if dv % 16 == 0 and dk % 16 == 0:
+        from kllm_b200.csrc.build import loaded_libraries
+        name = f"attention_tc-KLLM_HD{dk}" + ("" if dv == dk else f"-KLLM_VD{dv}")
+        assert name in loaded_libraries(), "the portions did not run on the tensor-core kernel"
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("H,dk,dr,dv,R", [(3, 16, 8, 12, 32), (5, 6, 2, 5, 10), (4, 32, 64, 32, 128), (1, 12, 6, 7, 22),
                                           (16, 64, 32, 64, 96), (40, 8, 4, 8, 16)])
