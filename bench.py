@@ -1192,8 +1192,10 @@ def design_comparison(args):
                 gu, dn = wsets[i % len(wsets)]
                 idx, wt = kernels.moe_route(x, router, top, score="softmax", renormalize=False, groups=groups, keep=keep)
                 offsets, perm = kernels.moe_sort(idx, E)
-                act = kernels.moe_gemm(x, gu, offsets, perm, wt, top, gated=True)
-                kernels.moe_combine(kernels.moe_gemm(act, dn, offsets, perm, wt, top, gated=False, scale_out=True), top)
+                # the route of parts/moe.py: large steps on the tcgen05 kernel, small ones on the grouped mma.sync kernel
+                mm = kernels.moe_gemm_tcgen05 if kernels.moe_gemm_tcgen05_pays(x, gu, perm.numel(), True, False) else kernels.moe_gemm
+                act = mm(x, gu, offsets, perm, wt, top, gated=True)
+                kernels.moe_combine(mm(act, dn, offsets, perm, wt, top, gated=False, scale_out=True), top)
             us = timed(experts, inner=2) * 1e3
             used = min(E, n * top)
             note(f"experts within groups ({top} of {E}, {keep} of {groups} groups) {name}", us, 3.0 * used * eff * width * esz,

@@ -1443,6 +1443,55 @@ def moe_gemm(a: torch.Tensor, w: torch.Tensor, offsets: torch.Tensor, perm: torc
     return c
 
 
+MOE_TCGEN05_ROWS = 64      # rows per expert on average from which a step's experts run on the tcgen05 kernel
+
+
+def moe_gemm_tcgen05_pays(a: torch.Tensor, w: torch.Tensor, rows: int, gated: bool, scale_in: bool) -> bool:
+    """Whether ``moe_gemm_tcgen05`` takes these operands and the step is large enough for tiles of 128
+    rows per expert: bfloat16, no weight on the experts' inputs (TMA brings the rows to the tensor
+    cores as they are), rows and matrices in whole 16-byte pieces."""
+    E, N, K = w.shape
+    if gated:
+        N //= 2
+    return (USE_TCGEN05 and a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and not scale_in and E <= 512
+            and rows >= 512 and rows >= MOE_TCGEN05_ROWS * E and K % 8 == 0 and N % 8 == 0 and w.is_contiguous()
+            and a.stride(1) == 1 and a.stride(0) % 8 == 0 and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+
+
+def moe_gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, offsets: torch.Tensor, perm: torch.Tensor, wt: torch.Tensor,
+                     top: int, gated: bool, scale_out: bool = False, activation: str = "silu", limit: float = 0.0,
+                     alpha: float = 1.0) -> torch.Tensor:
+    """``moe_gemm`` for large steps in bfloat16 on the tcgen05 tensor cores (csrc/moe_gemm_tcgen05.cu), same
+    operands and results; the weights may act on the experts' outputs only.  The gated form first gathers
+    the layer's input into sorted order, one row per (token, choice)."""
+    _cuda(a, w, offsets, perm, wt)
+    if activation not in _GATED_ACT or (activation == "clamped" and not limit > 0):
+        raise KernelError(f"moe_gemm: activation {activation!r} (silu, or clamped with a positive limit)")
+    _i32(offsets, "offsets"); _i32(perm, "perm")
+    rows = perm.numel()
+    E, N, K = w.shape
+    if gated:
+        N //= 2
+    if not moe_gemm_tcgen05_pays(a, w, rows, gated, False) or a.shape[1] != K:
+        raise KernelError("moe_gemm_tcgen05: operands not taken (bfloat16, rows of whole 16-byte pieces, a large step)")
+    if wt.dtype != torch.float32 or not wt.is_contiguous() or wt.numel() != rows:
+        raise KernelError("moe_gemm: one float32 weight per (token, choice)")
+    lib = load_library("moe_gemm_tcgen05")
+    if gated:
+        xs = torch.empty((rows, K), dtype=a.dtype, device=a.device)
+        rc = lib.kllm_moe_gather_sorted(_p(xs), _p(a), ctypes.c_int64(a.stride(0)), _p(perm), rows, int(top), K, _stream())
+        _check(lib, "moe_gemm_tcgen05", rc)
+        a = xs
+    elif not a.is_contiguous() or a.shape[0] != rows:
+        raise KernelError("moe_gemm_tcgen05: the sorted rows must be contiguous")
+    c = torch.empty((rows, N), dtype=a.dtype if gated else torch.float32, device=a.device)
+    rc = lib.kllm_moe_gemm_tcgen05(_p(c), _p(a), _p(w), _p(offsets), _p(perm), _p(wt), rows, E, N, K, int(gated),
+                                   int(scale_out), _GATED_ACT[activation], ctypes.c_float(limit), ctypes.c_float(alpha),
+                                   _p(status_word(a.device)), _stream())
+    _check(lib, "moe_gemm_tcgen05", rc)
+    return c
+
+
 def moe_combine(parts: torch.Tensor, top: int, shared: Optional[torch.Tensor] = None,
                 gate: Optional[torch.Tensor] = None, scale: float = 1.0) -> torch.Tensor:
     """y[t] = sum of parts[t * top + j] over j in order; float32.  With ``shared`` (float32

@@ -203,8 +203,13 @@ class RoutedExperts:
                                         self.groups_keep)
         offsets, perm = kernels.moe_sort(idx, self.experts)
         on_input = self.weight_on == "input"
-        act = kernels.moe_gemm(xn, self.w_gate_up, offsets, perm, wt, self.top, gated=True, scale_in=on_input, **self.act)
-        parts = kernels.moe_gemm(act, self.w_down, offsets, perm, wt, self.top, gated=False, scale_out=not on_input)
+        if kernels.moe_gemm_tcgen05_pays(xn, self.w_gate_up, perm.numel(), True, on_input):
+            # a large step in bfloat16: tiles of 128 rows per expert on the tcgen05 tensor cores
+            act = kernels.moe_gemm_tcgen05(xn, self.w_gate_up, offsets, perm, wt, self.top, gated=True, **self.act)
+            parts = kernels.moe_gemm_tcgen05(act, self.w_down, offsets, perm, wt, self.top, gated=False, scale_out=True)
+        else:
+            act = kernels.moe_gemm(xn, self.w_gate_up, offsets, perm, wt, self.top, gated=True, scale_in=on_input, **self.act)
+            parts = kernels.moe_gemm(act, self.w_down, offsets, perm, wt, self.top, gated=False, scale_out=not on_input)
         if self.shared is None:
             return kernels.moe_combine(parts, self.top)
         rows, logit = self._shared(xn)

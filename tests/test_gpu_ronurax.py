@@ -581,6 +581,59 @@ def test_router_with_groups(dtype, E, top, groups, keep):
     assert np.array_equal(idx0.cpu().numpy(), free)
 
 
+@pytest.mark.parametrize("n,E,top,d,f,act", [(700, 6, 3, 72, 104, "silu"), (1500, 4, 2, 128, 256, "silu"),
+                                             (520, 3, 1, 200, 40, "clamped"), (900, 8, 4, 64, 520, "silu")])
+def test_experts_of_a_large_step_on_the_tensor_cores(n, E, top, d, f, act):
+    """The experts' two products of a large bfloat16 step in tiles of 128 rows per expert: experts with no rows,
+    with a handful and with most of them, widths that end inside a k block and inside a 32-column chunk, weights
+    on the outputs; against the sums in double precision, pair by pair."""
+    import torch
+    from kllm_b200 import kernels
+    rng = np.random.default_rng(n + E)
+    h = P.round_bf16(rng.standard_normal((n, d)))
+    gate = P.round_bf16(rng.standard_normal((E, f, d)) / 6)
+    up = P.round_bf16(rng.standard_normal((E, f, d)) / 6)
+    down = P.round_bf16(rng.standard_normal((E, d, f)) / 5)
+    # the choice: expert 1 is never taken, expert 0 by five tokens, the rest unevenly
+    idx = np.zeros((n, top), dtype=np.int64)
+    others = [e for e in range(E) if e != 1]
+    weights_of = np.array([3.0 if e == others[-1] else 1.0 for e in others])
+    for t in range(n):
+        pool = others if t < 5 else others[1:]
+        pw = weights_of[len(others) - len(pool):]
+        idx[t] = rng.choice(pool, size=top, replace=False, p=pw / pw.sum()) if len(pool) >= top else rng.permutation(others)[:top]
+    wt = rng.uniform(0.05, 1.0, (n, top))
+    limit, alpha = (2.5, 1.7) if act == "clamped" else (0.0, 1.0)
+    want = np.zeros((n, d))
+    for e in range(E):
+        for j in range(top):
+            rows = np.nonzero(idx[:, j] == e)[0]
+            if not len(rows):
+                continue
+            g, u = h[rows] @ gate[e].T, h[rows] @ up[e].T
+            if act == "clamped":
+                g, u = np.minimum(g, limit), np.clip(u, -limit, limit)
+                a = g * P.sigmoid(alpha * g) * (u + 1.0)
+            else:
+                a = g * P.sigmoid(g) * u
+            want[rows] += wt[rows, j:j + 1] * (P.round_bf16(a) @ down[e].T)
+    gu = _t(np.concatenate([gate, up], axis=1), "bfloat16")
+    offsets, perm = kernels.moe_sort(_t(idx, "int32"), E)
+    wt_d = _t(wt.reshape(-1))
+    x = _t(h, "bfloat16")
+    assert kernels.moe_gemm_tcgen05_pays(x, gu, n * top, True, False)
+    kw = dict(activation=act, limit=limit, alpha=alpha)
+    a_s = kernels.moe_gemm_tcgen05(x, gu, offsets, perm, wt_d, top, gated=True, **kw)
+    parts = kernels.moe_gemm_tcgen05(a_s, _t(down, "bfloat16"), offsets, perm, wt_d, top, gated=False, scale_out=True)
+    kernels.check_status(x.device)
+    y = kernels.moe_combine(parts, top).cpu().numpy()
+    assert np.isfinite(y).all()
+    assert np.abs(y - want).max() <= 1e-2 * np.abs(want).max()
+    # the grouped mma.sync kernel gives the same rows but for the order of the sums
+    a_m = kernels.moe_gemm(x, gu, offsets, perm, wt_d, top, gated=True, **kw)
+    assert (a_m.float() - a_s.float()).abs().max().item() <= 2e-2 * a_m.float().abs().max().item()
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_sigmoid_gate_on_strided_rows(dtype):
     import torch
