@@ -541,6 +541,7 @@ def simt_fits(q: torch.Tensor, n_heads: int, n_kv: int, head_dim: int, v_head_di
 
 
 TC_HEAD_DIMS = tuple(range(16, 129, 16))     # head sizes of the tensor-core attention library
+WIDE_SINGLE_KEYS = 2048                      # a single token that sees at most this many keys runs as a row of the wide prefill form
 TC_WIDE_HEAD_DIMS = (160, 192, 224, 256)     # ... and those that only its unfused kernels are built for
 TCGEN05_HEAD_DIMS = (64, 128)                # head sizes of the tcgen05 prefill attention
 PREFETCH_L2 = os.environ.get("KLLM_B200_PREFETCH", "1") != "0"   # kernels warm L2 for the kernel after them
@@ -617,12 +618,17 @@ def attention(out: torch.Tensor, q: torch.Tensor, kcache: torch.Tensor, vcache: 
           and not (special and scale <= 0) and not segment and plain_values)
     # what the plain tensor-core route refuses, the prefill kernel takes in its wide form (bfloat16 rows, sizes
     # in steps of 16): portions go there, the single tokens at the head of the batch to the CUDA cores
+    # ... unless a segment or a window keeps every token's keys few: then a single token's CTA has a short walk
+    # and the tensor-core kernel takes the whole step, decoding steps too
     wide = (not tc and q.dtype == torch.bfloat16 and (head_dim in TC_HEAD_DIMS or head_dim in TC_WIDE_HEAD_DIMS)
             and vd % 16 == 0 and 16 <= vd <= 256 and group <= 64 and not (special and scale <= 0)
-            and vcache.dim() == 4 and vcache.shape[3] % 8 == 0 and not ctx.all_single and bool(ctx.host_n_new))
+            and vcache.dim() == 4 and vcache.shape[3] % 8 == 0)
+    short = min(int(segment or (1 << 30)), int(window or (1 << 30))) <= WIDE_SINGLE_KEYS
+    if wide and not short and (ctx.all_single or not ctx.host_n_new):
+        wide = False
     if wide:
         singles = 0
-        while singles < ctx.n_requests and ctx.host_n_new[singles] == 1:
+        while not short and singles < ctx.n_requests and ctx.host_n_new[singles] == 1:
             singles += 1
         if singles:
             if not simt_fits(q, n_heads, n_kv, head_dim, vd):
