@@ -32,27 +32,49 @@ KLLM_EXPORT_LAST_ERROR(moe)
 namespace {
 
 // ---- router ----------------------------------------------------------------------
-// one warp per token; E logits in shared memory (E <= 1024).
+// one CTA of four warps per token: the warps share the columns of the router's rows, so that a step of
+// few tokens still has many loads in flight (the router's rows come from HBM in every decode step: the
+// weights streamed between two steps push them out of L2); warp 0 then makes the choice.  E logits in
+// shared memory (E <= 1024).  A logit's sum has one order, fixed by the width.
 template <typename T>
 __global__ void __launch_bounds__(128)
 route_kernel(int* __restrict__ idx, float* __restrict__ wt, const T* __restrict__ h, const float* __restrict__ router,
              int n, int d, int E, int top, int softmax, int renorm, int groups, int keep) {
-    extern __shared__ float zsh[];            // [4 warps][E], then [4 warps][2 * groups] when groups limit the choice
+    extern __shared__ float zsh[];            // [E], then [2 * groups] when groups limit the choice
+    __shared__ float part[4][8];
     griddep_wait();
     griddep_launch();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int t = blockIdx.x * 4 + warp;
-    if (t >= n) return;
-    float* z = zsh + warp * E;
+    const int t = blockIdx.x;
+    float* z = zsh;
     const T* hr = h + (int64_t)t * d;
-    for (int e = 0; e < E; e++) {
-        const float* wr = router + (int64_t)e * d;
-        float acc = 0.f;
-        for (int c = lane; c < d; c += 32) acc += to_f32(hr[c]) * wr[c];
-        acc = warp_sum(acc);
-        if (lane == 0) z[e] = acc;
+    // eight experts at a time: their loads are independent of one another, and the token's row is read
+    // once for all eight; every expert's sum still runs over its columns in the one order
+    for (int e0 = 0; e0 < E; e0 += 8) {
+        const float* wr[8];
+        float acc[8];
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+            wr[j] = router + (int64_t)min(e0 + j, E - 1) * d;
+            acc[j] = 0.f;
+        }
+#pragma unroll 4
+        for (int c = threadIdx.x; c < d; c += 128) {
+            const float hv = to_f32(hr[c]);
+#pragma unroll
+            for (int j = 0; j < 8; j++) acc[j] += hv * wr[j][c];
+        }
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+            const float a = warp_sum(acc[j]);
+            if (lane == 0) part[warp][j] = a;
+        }
+        __syncthreads();
+        if (threadIdx.x < 8 && e0 + threadIdx.x < E)
+            z[e0 + threadIdx.x] = (part[0][threadIdx.x] + part[1][threadIdx.x]) + (part[2][threadIdx.x] + part[3][threadIdx.x]);
+        __syncthreads();
     }
-    __syncwarp();
+    if (warp != 0) return;
     // the choice is made among the logits: both scores grow with them, and a sigmoid that has
     // reached 1.0f no longer tells two experts apart
     float zmax = 0.f, zsum = 1.f;
@@ -68,7 +90,7 @@ route_kernel(int* __restrict__ idx, float* __restrict__ wt, const T* __restrict_
         // The experts form `groups` equal groups of neighbours; a group's score is its best expert's
         // (the logits order as the scores do).  Only experts of the `keep` best groups can be chosen,
         // the lower group first among equals; the scores themselves stay those over all experts.
-        float* gb = zsh + 4 * E + warp * 2 * groups;      // a group's best logit, then whether it is kept
+        float* gb = zsh + E;                              // a group's best logit, then whether it is kept
         const int per = E / groups;
         for (int gi = lane; gi < groups; gi += 32) {
             float b = -INFINITY;
@@ -470,12 +492,12 @@ extern "C" int kllm_moe_route(int* idx, float* wt, const void* h, const float* r
     if (E % groups || keep < 1 || keep > groups || top > keep * (E / groups))
         KLLM_FAIL("moe route: %d of %d experts in %d groups of which %d are kept", top, E, groups, keep);
     cudaStream_t s = (cudaStream_t)stream;
-    const size_t smem = (size_t)4 * (E + 2 * groups) * sizeof(float);
+    const size_t smem = (size_t)(E + 2 * groups) * sizeof(float);
     if (dtype == KLLM_F32)
-        kllm_launch((route_kernel<float>), dim3((n + 3) / 4), dim3(128), smem, s, idx, wt, (const float*)h, router, n, d, E,
+        kllm_launch((route_kernel<float>), dim3(n), dim3(128), smem, s, idx, wt, (const float*)h, router, n, d, E,
                     top, softmax, renorm, groups, keep);
     else if (dtype == KLLM_BF16)
-        kllm_launch((route_kernel<bf16>), dim3((n + 3) / 4), dim3(128), smem, s, idx, wt, (const bf16*)h, router, n, d, E,
+        kllm_launch((route_kernel<bf16>), dim3(n), dim3(128), smem, s, idx, wt, (const bf16*)h, router, n, d, E,
                     top, softmax, renorm, groups, keep);
     else
         KLLM_FAIL("moe route: unknown element type %d", dtype);

@@ -241,6 +241,70 @@ add_layernorm_kernel(float* __restrict__ x, const R* __restrict__ res, T* __rest
     }
 }
 
+// The common case of a step's rows (every row, float32 residual or none, width a multiple of 4 up
+// to kThreads * 4 * kVec) in one pass over the memory: a thread keeps its elements in registers
+// between the sum, the sum of squared deviations and the scaling, 16-byte accesses.  Whether this
+// kernel runs is decided by the width and the addresses alone, never by the number of rows.
+template <typename T>
+__global__ void __launch_bounds__(kThreads)
+add_layernorm_vec4_kernel(float* __restrict__ x, const float* __restrict__ res, T* __restrict__ out,
+                          const float* __restrict__ gain, const float* __restrict__ bias, int d, float eps) {
+    __shared__ float red[32];
+    griddep_wait();
+    griddep_launch();
+    const int r = blockIdx.x;
+    float4* xr = reinterpret_cast<float4*>(x + (int64_t)r * d);
+    const float4* rr = res ? reinterpret_cast<const float4*>(res + (int64_t)r * d) : nullptr;
+    const float4* g4 = reinterpret_cast<const float4*>(gain);
+    const float4* b4 = reinterpret_cast<const float4*>(bias);
+    const int n4 = d >> 2;
+    float4 v[kVec];
+    float sum = 0.f;
+#pragma unroll
+    for (int k = 0; k < kVec; k++) {
+        const int i = threadIdx.x + k * kThreads;
+        if (i < n4) {
+            v[k] = xr[i];
+            if (rr) {
+                const float4 a = rr[i];
+                v[k].x += a.x; v[k].y += a.y; v[k].z += a.z; v[k].w += a.w;
+                xr[i] = v[k];
+            }
+            sum += (v[k].x + v[k].y) + (v[k].z + v[k].w);
+        }
+    }
+    const float mean = block_sum(sum, red) / (float)d;
+    float sq = 0.f;
+#pragma unroll
+    for (int k = 0; k < kVec; k++) {
+        const int i = threadIdx.x + k * kThreads;
+        if (i < n4) {
+            v[k].x -= mean; v[k].y -= mean; v[k].z -= mean; v[k].w -= mean;
+            sq += (v[k].x * v[k].x + v[k].y * v[k].y) + (v[k].z * v[k].z + v[k].w * v[k].w);
+        }
+    }
+    const float scale = rsqrtf(block_sum(sq, red) / (float)d + eps);
+#pragma unroll
+    for (int k = 0; k < kVec; k++) {
+        const int i = threadIdx.x + k * kThreads;
+        if (i < n4) {
+            const float4 g = g4[i], b = b4[i];
+            const float o0 = v[k].x * scale * g.x + b.x, o1 = v[k].y * scale * g.y + b.y;
+            const float o2 = v[k].z * scale * g.z + b.z, o3 = v[k].w * scale * g.w + b.w;
+            if (sizeof(T) == 4) {
+                reinterpret_cast<float4*>(out + (int64_t)r * d)[i] = make_float4(o0, o1, o2, o3);
+            } else {
+                __nv_bfloat162 lo = __floats2bfloat162_rn(o0, o1);
+                __nv_bfloat162 hi = __floats2bfloat162_rn(o2, o3);
+                uint2 pk;
+                pk.x = *reinterpret_cast<uint32_t*>(&lo);
+                pk.y = *reinterpret_cast<uint32_t*>(&hi);
+                reinterpret_cast<uint2*>(out + (int64_t)r * d)[i] = pk;
+            }
+        }
+    }
+}
+
 }  // namespace
 
 // x float32 [n][d] (updated), y float32 [n][d], gain float32 [d]; out (optional, element type
@@ -307,6 +371,18 @@ extern "C" int kllm_add_layernorm(void* x, const void* res, void* out, const voi
     if (!gain || !bias) KLLM_FAIL("layernorm: gain and bias are required");
     cudaStream_t s = (cudaStream_t)stream;
     const int threads = d <= 512 ? 64 : (d <= 2048 ? 128 : kThreads);
+    auto aligned = [](const void* p) { return ((uintptr_t)p & 15) == 0; };
+    if ((res == nullptr || res_dtype == KLLM_F32) && rows == nullptr && (d & 3) == 0 && d <= kThreads * 4 * kVec &&
+        aligned(x) && aligned(res) && aligned(gain) && aligned(bias) && aligned(out) &&
+        (dtype == KLLM_BF16 || dtype == KLLM_F32)) {
+        if (dtype == KLLM_BF16)
+            kllm_launch((add_layernorm_vec4_kernel<bf16>), dim3(n_rows), dim3(kThreads), 0, s, (float*)x, (const float*)res,
+                        (bf16*)out, (const float*)gain, (const float*)bias, d, eps);
+        else
+            kllm_launch((add_layernorm_vec4_kernel<float>), dim3(n_rows), dim3(kThreads), 0, s, (float*)x, (const float*)res,
+                        (float*)out, (const float*)gain, (const float*)bias, d, eps);
+        KLLM_LAUNCH_STATUS();
+    }
     if (res == nullptr) res_dtype = dtype;
 #define KLLM_LN(T, R)                                                                                           \
     kllm_launch((add_layernorm_kernel<T, R>), dim3(n_rows), dim3(threads), 0, s, (float*)x, (const R*)res, (T*)out, \

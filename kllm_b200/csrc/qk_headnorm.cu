@@ -26,7 +26,7 @@ KLLM_EXPORT_LAST_ERROR(qk_headnorm)
 
 namespace {
 
-constexpr int kWarps = 4, kMaxDk = 512, kMaxRot = 512;
+constexpr int kWarps = 8, kMaxDk = 512, kMaxRot = 512;
 
 template <typename T>
 __global__ void __launch_bounds__(kWarps * 32)

@@ -136,7 +136,8 @@ def test_whole_prompt_and_every_way_of_cutting(tmp_path, name, dtype):
             got = run_cut(eng, ids, cuts)
             check_rows(got, want, dtype, f"{name} portions {cuts}")
             if dtype == "float32":
-                assert np.abs(got - whole).max() <= 1e-5 * np.abs(want).max(), cuts
+                # small steps take other product kernels (rows by FMAs) than large ones (SGEMM): sums in another order
+                assert np.abs(got - whole).max() <= 3e-5 * np.abs(want).max(), cuts
         eng.cache.audit()
     finally:
         eng.close()
