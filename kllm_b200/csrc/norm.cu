@@ -241,20 +241,23 @@ add_layernorm_kernel(float* __restrict__ x, const R* __restrict__ res, T* __rest
     }
 }
 
-// The common case of a step's rows (every row, float32 residual or none, width a multiple of 4 up
-// to kThreads * 4 * kVec) in one pass over the memory: a thread keeps its elements in registers
+// The common case of a step's rows (float32 residual or none, width a multiple of 4 up
+// to kThreads * 4 * kVec; every row, or the rows that `rows` names, which are then left as they are) in one
+// pass over the memory: a thread keeps its elements in registers
 // between the sum, the sum of squared deviations and the scaling, 16-byte accesses.  Whether this
 // kernel runs is decided by the width and the addresses alone, never by the number of rows.
 template <typename T>
 __global__ void __launch_bounds__(kThreads)
 add_layernorm_vec4_kernel(float* __restrict__ x, const float* __restrict__ res, T* __restrict__ out,
-                          const float* __restrict__ gain, const float* __restrict__ bias, int d, float eps) {
+                          const float* __restrict__ gain, const float* __restrict__ bias,
+                          const int* __restrict__ rows, int d, float eps) {
     __shared__ float red[32];
     griddep_wait();
     griddep_launch();
     const int r = blockIdx.x;
-    float4* xr = reinterpret_cast<float4*>(x + (int64_t)r * d);
-    const float4* rr = res ? reinterpret_cast<const float4*>(res + (int64_t)r * d) : nullptr;
+    const int64_t src = rows ? (int64_t)rows[r] : (int64_t)r;
+    float4* xr = reinterpret_cast<float4*>(x + src * d);
+    const float4* rr = res ? reinterpret_cast<const float4*>(res + src * d) : nullptr;
     const float4* g4 = reinterpret_cast<const float4*>(gain);
     const float4* b4 = reinterpret_cast<const float4*>(bias);
     const int n4 = d >> 2;
@@ -268,7 +271,7 @@ add_layernorm_vec4_kernel(float* __restrict__ x, const float* __restrict__ res, 
             if (rr) {
                 const float4 a = rr[i];
                 v[k].x += a.x; v[k].y += a.y; v[k].z += a.z; v[k].w += a.w;
-                xr[i] = v[k];
+                if (!rows) xr[i] = v[k];
             }
             sum += (v[k].x + v[k].y) + (v[k].z + v[k].w);
         }
@@ -372,15 +375,15 @@ extern "C" int kllm_add_layernorm(void* x, const void* res, void* out, const voi
     cudaStream_t s = (cudaStream_t)stream;
     const int threads = d <= 512 ? 64 : (d <= 2048 ? 128 : kThreads);
     auto aligned = [](const void* p) { return ((uintptr_t)p & 15) == 0; };
-    if ((res == nullptr || res_dtype == KLLM_F32) && rows == nullptr && (d & 3) == 0 && d <= kThreads * 4 * kVec &&
+    if ((res == nullptr || res_dtype == KLLM_F32) && (d & 3) == 0 && d <= kThreads * 4 * kVec &&
         aligned(x) && aligned(res) && aligned(gain) && aligned(bias) && aligned(out) &&
         (dtype == KLLM_BF16 || dtype == KLLM_F32)) {
         if (dtype == KLLM_BF16)
             kllm_launch((add_layernorm_vec4_kernel<bf16>), dim3(n_rows), dim3(kThreads), 0, s, (float*)x, (const float*)res,
-                        (bf16*)out, (const float*)gain, (const float*)bias, d, eps);
+                        (bf16*)out, (const float*)gain, (const float*)bias, rows, d, eps);
         else
             kllm_launch((add_layernorm_vec4_kernel<float>), dim3(n_rows), dim3(kThreads), 0, s, (float*)x, (const float*)res,
-                        (float*)out, (const float*)gain, (const float*)bias, d, eps);
+                        (float*)out, (const float*)gain, (const float*)bias, rows, d, eps);
         KLLM_LAUNCH_STATUS();
     }
     if (res == nullptr) res_dtype = dtype;
