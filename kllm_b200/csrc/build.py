@@ -222,7 +222,10 @@ def loaded_libraries() -> Dict[str, "CheckedLibrary"]:
 
 # Libraries that are built once per value of a compile-time size: build_all()
 # compiles every allowed value, a running process only the one its model has.
-VARIANTS = {"attention_tc": [{"KLLM_HD": hd} for hd in list(range(16, 129, 16)) + [160, 192, 224, 256]],
+# The wide form of the attention library (values of another size than the keys) is built per pair of
+# sizes at first use; build_all() compiles the pairs below so that the form itself is checked.
+VARIANTS = {"attention_tc": [{"KLLM_HD": hd} for hd in list(range(16, 129, 16)) + [160, 192, 224, 256]]
+            + [{"KLLM_HD": hd, "KLLM_VD": vd} for hd, vd in ((32, 64), (64, 128), (128, 64), (128, 256))],
             "attention_tcgen05": [{"KLLM_HD": hd} for hd in (64, 128)],
             "attention_tcgen05_ptmem": [{"KLLM_HD": hd} for hd in (64, 128)]}
 
