@@ -660,6 +660,10 @@ attn_prefill_kernel(void* __restrict__ out_, const bf16* __restrict__ q, int64_t
     const int* table = block_table + (int64_t)req * max_blocks;
     const int ntiles = (hi - lo + TILE - 1) / TILE;
 
+    // A tile whose rows all fit one warp (a decoding token's heads): every warp takes the same rows and every
+    // fourth key tile, with a running (max, sum, output) of its own; the four are merged at the end in warp order.
+    const bool spread = n_tok * gs <= 16 * MT;
+    const int wrow0 = spread ? 0 : 16 * MT * warp;
     // this thread's rows, two per MMA tile: (token, head of the group)
     int pr[MT][2], wr[MT][2];            // position of the row's token (-1: row unused), first visible key
     bool vr[MT][2];
@@ -672,7 +676,7 @@ attn_prefill_kernel(void* __restrict__ out_, const bf16* __restrict__ q, int64_t
         const bf16* qp[2];
 #pragma unroll
         for (int h = 0; h < 2; h++) {
-            const int r = (16 * MT) * warp + 16 * m + gid + 8 * h;
+            const int r = wrow0 + 16 * m + gid + 8 * h;
             const int tt = r / gs, hh = r - tt * gs;
             vr[m][h] = tt < n_tok;
             pr[m][h] = vr[m][h] ? pos0 + tt : -1;
@@ -693,7 +697,6 @@ attn_prefill_kernel(void* __restrict__ out_, const bf16* __restrict__ q, int64_t
         }
     }
     // key range that this warp's rows can see at all
-    const int wrow0 = 16 * MT * warp;
     const int wt_first = wrow0 / gs, wt_last = min(n_tok - 1, (wrow0 + 16 * MT - 1) / gs);
     const bool warp_active = wt_first < n_tok;
     const int warp_hi = pos0 + wt_last + 1;
@@ -719,6 +722,7 @@ attn_prefill_kernel(void* __restrict__ out_, const bf16* __restrict__ q, int64_t
             for (int j = 0; j < 4; j++) o[m][i][j] = 0.f;
         // a sink starts the running maximum and counts 1 in the sum (the sums are per lane and
         // meet at the end: one lane of the row's four holds it)
+        if (spread && warp > 0) sk_[m][0] = sk_[m][1] = -INFINITY;      // one warp counts the sink
         mx[m][0] = sk_[m][0]; mx[m][1] = sk_[m][1];
         l[m][0] = (tq == 0 && sk_[m][0] > -INFINITY) ? 1.f : 0.f;
         l[m][1] = (tq == 0 && sk_[m][1] > -INFINITY) ? 1.f : 0.f;
@@ -747,6 +751,7 @@ attn_prefill_kernel(void* __restrict__ out_, const bf16* __restrict__ q, int64_t
         const bf16* sv = sk + TILE * ROW;
         const int key0 = lo + i * TILE;
         if (!warp_active || key0 >= warp_hi || key0 + TILE <= warp_lo) continue;   // nothing of this tile is visible to the warp
+        if (spread && (i & 3) != warp) continue;                                   // another warp's tile
         const bool need_mask = key0 < warp_lo_last || key0 + TILE - 1 > warp_full_below;
         // scores of the warp's rows against the 64 keys: every key fragment serves all MT tiles
         float s[MT][8][4];
@@ -863,13 +868,70 @@ attn_prefill_kernel(void* __restrict__ out_, const bf16* __restrict__ q, int64_t
         }
     }
     cp_async_wait<0>();
+    if (spread) {
+        // the warps' partial results meet in the shared memory that held the tiles: per warp and row the
+        // maximum, the sum and VD outputs.  Warp 0 merges them in warp order.
+        __syncthreads();
+        float* part = reinterpret_cast<float*>(smem_raw);
+        constexpr int PW = VD + 2;
+#pragma unroll
+        for (int m = 0; m < MT; m++)
+#pragma unroll
+            for (int h = 0; h < 2; h++) {
+                float lv = l[m][h];
+                lv += __shfl_xor_sync(0xffffffffu, lv, 1);
+                lv += __shfl_xor_sync(0xffffffffu, lv, 2);
+                l[m][h] = lv;
+                float* pr_ = part + (int64_t)(warp * 16 * MT + 16 * m + gid + 8 * h) * PW;
+                if (tq == 0) { pr_[0] = mx[m][h]; pr_[1] = lv; }
+#pragma unroll
+                for (int dt = 0; dt < DTILES; dt++) {
+                    pr_[2 + dt * 8 + 2 * tq] = o[m][dt][2 * h];
+                    pr_[2 + dt * 8 + 2 * tq + 1] = o[m][dt][2 * h + 1];
+                }
+            }
+        __syncthreads();
+        if (warp > 0) return;
+#pragma unroll
+        for (int m = 0; m < MT; m++)
+#pragma unroll
+            for (int h = 0; h < 2; h++) {
+                const float* p0 = part + (int64_t)(16 * m + gid + 8 * h) * PW;
+                float M = -INFINITY;
+#pragma unroll
+                for (int w = 0; w < 4; w++) M = fmaxf(M, p0[(int64_t)w * 16 * MT * PW]);
+                const float base = (M == -INFINITY) ? 0.f : M;
+                float f[4], L = 0.f;
+#pragma unroll
+                for (int w = 0; w < 4; w++) {
+                    const float* pw = p0 + (int64_t)w * 16 * MT * PW;
+                    f[w] = exp2f((pw[0] - base) * scale_log2e);
+                    L += pw[1] * f[w];
+                }
+                l[m][h] = L;
+#pragma unroll
+                for (int dt = 0; dt < DTILES; dt++) {
+                    float a = 0.f, b = 0.f;
+#pragma unroll
+                    for (int w = 0; w < 4; w++) {
+                        const float* pw = p0 + (int64_t)w * 16 * MT * PW + 2 + dt * 8 + 2 * tq;
+                        a += pw[0] * f[w];
+                        b += pw[1] * f[w];
+                    }
+                    o[m][dt][2 * h] = a;
+                    o[m][dt][2 * h + 1] = b;
+                }
+            }
+    }
 #pragma unroll
     for (int m = 0; m < MT; m++) {
 #pragma unroll
         for (int h = 0; h < 2; h++) {
             float lv = l[m][h];
-            lv += __shfl_xor_sync(0xffffffffu, lv, 1);
-            lv += __shfl_xor_sync(0xffffffffu, lv, 2);
+            if (!spread) {
+                lv += __shfl_xor_sync(0xffffffffu, lv, 1);
+                lv += __shfl_xor_sync(0xffffffffu, lv, 2);
+            }
             if (!vr[m][h]) continue;
             const float inv = 1.f / lv;
             if (out_f32) {
