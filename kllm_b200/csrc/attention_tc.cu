@@ -152,6 +152,26 @@ __device__ __forceinline__ void load_tile_wide(bf16* stage, const bf16* __restri
                                                int page_size) {
     bf16* sk = stage;
     bf16* sv = stage + TILE * ROW;
+    const int lp0 = key0 / page_size, in_page = key0 - lp0 * page_size;
+    if (in_page + TILE <= page_size) {
+        // the whole tile lies in one page: one look-up, rows one after the other
+        const int64_t page = table[lp0];
+        const int64_t kbase = ((page * n_kv + g) * page_size + in_page) * HD;
+        const int64_t vbase = ((page * v_heads + gv) * page_size + in_page) * v_row;
+#pragma unroll
+        for (int c = threadIdx.x; c < TILE * CHUNKS; c += THREADS) {
+            const int row = c / CHUNKS, ch = c - row * CHUNKS;
+            const bool valid = key0 + row < hi;
+            cp_async16(sk + row * ROW + ch * 8, kcache + (valid ? kbase + row * HD + ch * 8 : 0), valid);
+        }
+#pragma unroll
+        for (int c = threadIdx.x; c < TILE * VCHUNKS; c += THREADS) {
+            const int row = c / VCHUNKS, ch = c - row * VCHUNKS;
+            const bool valid = key0 + row < hi;
+            cp_async16(sv + row * ROWV + ch * 8, vcache + (valid ? vbase + (int64_t)row * v_row + ch * 8 : 0), valid);
+        }
+        return;
+    }
     for (int c = threadIdx.x; c < TILE * CHUNKS; c += THREADS) {
         const int row = c / CHUNKS, ch = c - row * CHUNKS;
         const int key = key0 + row;
