@@ -1455,12 +1455,14 @@ MOE_TCGEN05_ROWS = 64      # rows per expert on average from which a step's expe
 def moe_gemm_tcgen05_pays(a: torch.Tensor, w: torch.Tensor, rows: int, gated: bool, scale_in: bool) -> bool:
     """Whether ``moe_gemm_tcgen05`` takes these operands and the step is large enough for tiles of 128
     rows per expert: bfloat16, no weight on the experts' inputs (TMA brings the rows to the tensor
-    cores as they are), rows and matrices in whole 16-byte pieces."""
+    cores as they are), rows and matrices in whole 16-byte pieces and at least as wide as one 64-column k
+    block (a layer's two products have the same two widths, so one answer holds for both)."""
     E, N, K = w.shape
     if gated:
         N //= 2
     return (USE_TCGEN05 and a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and not scale_in and E <= 512
-            and rows >= 512 and rows >= MOE_TCGEN05_ROWS * E and K % 8 == 0 and N % 8 == 0 and w.is_contiguous()
+            and rows >= 512 and rows >= MOE_TCGEN05_ROWS * E and K % 8 == 0 and N % 8 == 0 and min(K, N) >= 64
+            and w.is_contiguous()
             and a.stride(1) == 1 and a.stride(0) % 8 == 0 and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
 
 

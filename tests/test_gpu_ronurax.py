@@ -583,7 +583,7 @@ def test_router_with_groups(dtype, E, top, groups, keep):
 
 
 @pytest.mark.parametrize("n,E,top,d,f,act", [(700, 6, 3, 72, 104, "silu"), (1500, 4, 2, 128, 256, "silu"),
-                                             (520, 3, 1, 200, 40, "clamped"), (900, 8, 4, 64, 520, "silu")])
+                                             (520, 3, 1, 200, 72, "clamped"), (600, 4, 2, 64, 64, "silu"), (900, 8, 4, 64, 520, "silu")])
 def test_experts_of_a_large_step_on_the_tensor_cores(n, E, top, d, f, act):
     """The experts' two products of a large bfloat16 step in tiles of 128 rows per expert: experts with no rows,
     with a handful and with most of them, widths that end inside a k block and inside a 32-column chunk, weights
