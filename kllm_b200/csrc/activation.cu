@@ -86,10 +86,12 @@ __global__ void clamped_glu_kernel(T* __restrict__ out, int64_t out_stride, cons
     }
 }
 
-// out = f(in) elementwise on float32 input rows: op 0 the square of relu, op 1 tanh.
+// out = f(in) elementwise on float32 input rows: op 0 the square of relu, op 1 tanh, op 2 the value itself
+// (a change of element type), op 3 the gelu with the error function, op 4 the gelu with tanh
+// (0.5 z (1 + tanh(sqrt(2 / pi) (z + 0.044715 z^3)))), op 5 arg * tanh(z / arg) (a soft cap at +-arg).
 template <typename T>
 __global__ void unary_kernel(T* __restrict__ out, int64_t out_stride, const float* __restrict__ in, int64_t in_stride,
-                             int n, int f, int op) {
+                             int n, int f, int op, float arg) {
     griddep_wait();
     griddep_launch();
     const int64_t total = (int64_t)n * f;
@@ -102,8 +104,16 @@ __global__ void unary_kernel(T* __restrict__ out, int64_t out_stride, const floa
         if (op == 0) {
             const float p = fmaxf(z, 0.f);
             v = p * p;
-        } else {
+        } else if (op == 1) {
             v = tanhf(z);
+        } else if (op == 2) {
+            v = z;
+        } else if (op == 3) {
+            v = 0.5f * z * (1.f + erff(z * 0.70710678118654752f));
+        } else if (op == 4) {
+            v = 0.5f * z * (1.f + tanhf(0.79788456080286536f * (z + 0.044715f * z * z * z)));
+        } else {
+            v = arg * tanhf(z / arg);
         }
         out[r * out_stride + c] = from_f32<T>(v);
     }
@@ -113,18 +123,19 @@ __global__ void unary_kernel(T* __restrict__ out, int64_t out_stride, const floa
 
 // out [n][f] in the element type `dtype`, in float32 [n][f], dense rows at their strides.
 extern "C" int kllm_unary(void* out, int64_t out_stride, const void* in, int64_t in_stride, int n, int f, int op,
-                          int dtype, void* stream) {
+                          float arg, int dtype, void* stream) {
     if (n <= 0 || f <= 0) return 0;
-    if (op < 0 || op > 1) KLLM_FAIL("unary: unknown function %d", op);
+    if (op < 0 || op > 5) KLLM_FAIL("unary: unknown function %d", op);
+    if (op == 5 && !(arg > 0.f)) KLLM_FAIL("unary: a soft cap must be positive");
     cudaStream_t s = (cudaStream_t)stream;
     int64_t blocks = ((int64_t)n * f + 255) / 256;
     if (blocks > 148 * 16) blocks = 148 * 16;
     if (dtype == KLLM_F32)
         kllm_launch((unary_kernel<float>), dim3((unsigned)blocks), dim3(256), 0, s, (float*)out, out_stride,
-                    (const float*)in, in_stride, n, f, op);
+                    (const float*)in, in_stride, n, f, op, arg);
     else if (dtype == KLLM_BF16)
         kllm_launch((unary_kernel<bf16>), dim3((unsigned)blocks), dim3(256), 0, s, (bf16*)out, out_stride,
-                    (const float*)in, in_stride, n, f, op);
+                    (const float*)in, in_stride, n, f, op, arg);
     else
         KLLM_FAIL("unary: unknown element type %d", dtype);
     KLLM_LAUNCH_STATUS();

@@ -1,0 +1,274 @@
+// Attention whose scores are mixed across the heads before the softmax, over a paged cache, for mixed
+// batches of prompt portions and single tokens.
+//
+// With H query heads on G key/value heads (head h reads kv head h / (H / G)), a matrix M [H][H], a
+// window W (0: none) and optional sinks:
+//
+//     raw_g(i, j)   = scale * q_g(i) . k_kv(g)(j)                  for every head g
+//     s_h(i, j)     = sum over g of M[h][g] raw_g(i, j)            the mixing, before mask and softmax
+//     visible       : j <= i and (W == 0 or i - j < W)
+//     p_h(i, j)     = exp(s_h(i, j)) / (exp(sink_h) + sum over visible j' of exp(s_h(i, j')))
+//     out_h(i)      = sum over visible j of p_h(i, j) v_kv(h)(j)
+//
+// (without sinks the first term of the denominator is absent).  Since every head's score needs all
+// heads' raw scores, a CTA holds ALL heads of a tile of query rows: it walks the visible keys in tiles,
+// forms the raw scores of all heads for the tile, mixes them, and keeps a running maximum, denominator
+// and output per (head, row) as in any streaming softmax.  Scores, mixing, weights and sums are float32
+// in both element types; queries, keys and values are widened when they are brought into shared memory.
+// The sums of a row run over the keys in ascending order in tiles that start at the first key its
+// tile's first row sees, so a row's result depends on how its prompt was cut only through the order of
+// float32 additions.
+//
+// Work per key tile, all in shared memory:  (1) K tile in;  (2) raw scores, a thread per (kv head, row,
+// key) computing the scores of that kv head's query heads with one pass over the key;  (3) V tile in over the
+// K tile, and the mixing, a thread per (four heads, row, key);  (4) one warp per (head, row): maximum,
+// weights, denominator;  (5) the output, a thread per (head, value channel) for all rows of the tile.
+#include "common.cuh"
+
+KLLM_EXPORT_LAST_ERROR(attention_mixed)
+
+namespace {
+
+constexpr int kThreads = 256;
+constexpr int kMaxPer = 16;     // query heads on a kv head that one thread scores together
+constexpr int kMaxTQ = 8;       // rows of a tile
+
+struct Shape {
+    int H, G, dk, dv, TQ, TK;
+};
+
+__host__ __device__ inline size_t smem_floats(const Shape& s) {
+    const size_t kv = (size_t)s.TK * (size_t)((s.G * s.dk > s.G * s.dv ? s.G * s.dk : s.G * s.dv) + 1);
+    return (size_t)s.TQ * s.H * s.dk            // q
+           + (size_t)s.H * s.H                  // M
+           + kv                                 // K tile, then V tile
+           + 2 * (size_t)s.H * s.TQ * s.TK      // raw, mixed / weights
+           + 3 * (size_t)s.H * s.TQ             // maximum, denominator, correction
+           + (size_t)s.TQ * s.H * s.dv;         // output
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kThreads)
+attention_mixed_kernel(T* __restrict__ out, const T* __restrict__ q, int64_t q_stride, const T* __restrict__ kcache,
+                       const T* __restrict__ vcache, const float* __restrict__ mix, const float* __restrict__ sinks,
+                       const int* __restrict__ q_start, const int* __restrict__ start_pos,
+                       const int* __restrict__ block_table, int max_blocks, int n_requests, Shape sh, int page_size,
+                       int window, float scale) {
+    extern __shared__ float sm[];
+    const int H = sh.H, G = sh.G, dk = sh.dk, dv = sh.dv, TQ = sh.TQ, TK = sh.TK;
+    const int per = H / G;
+    const int kw = G * dk, vw = G * dv;
+    const int kp = (kw > vw ? kw : vw) + 1;                 // pitch of the K / V tile: odd, so that keys fall into different banks
+    float* qs = sm;                                         // [TQ][H * dk], scaled
+    float* ms = qs + (size_t)TQ * H * dk;                   // [H][H]
+    float* kt = ms + H * H;                                 // [TK][kp]
+    float* raw = kt + (size_t)TK * kp;                      // [H][TQ][TK]
+    float* pr = raw + (size_t)H * TQ * TK;                  // [H][TQ][TK]: mixed scores, then weights
+    float* mx = pr + (size_t)H * TQ * TK;                   // [H][TQ]
+    float* dn = mx + H * TQ;                                // [H][TQ]
+    float* cr = dn + H * TQ;                                // [H][TQ]
+    float* acc = cr + H * TQ;                               // [TQ][H * dv]
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+
+    for (int i = tid; i < H * H; i += kThreads) ms[i] = mix[i];
+    griddep_wait();
+    griddep_launch();
+    // which request and which of its tiles
+    int req = 0, tile = blockIdx.x;
+    for (; req < n_requests; req++) {
+        const int tiles = (q_start[req + 1] - q_start[req] + TQ - 1) / TQ;
+        if (tile < tiles) break;
+        tile -= tiles;
+    }
+    if (req >= n_requests) return;
+    const int row0 = q_start[req] + tile * TQ;
+    const int nq = min(TQ, q_start[req + 1] - row0);
+    const int p0 = start_pos[req] + tile * TQ;              // position of the tile's first row
+    const int hi = p0 + nq - 1;                             // last key any row sees
+    const int lo = window > 0 ? max(0, p0 - window + 1) : 0;
+    const int* table = block_table + (int64_t)req * max_blocks;
+
+    for (int i = tid; i < nq * H * dk; i += kThreads) {
+        const int r = i / (H * dk), c = i - r * (H * dk);
+        qs[i] = to_f32(q[(int64_t)(row0 + r) * q_stride + c]) * scale;
+    }
+    for (int i = tid; i < H * TQ; i += kThreads) {
+        const int h = i / TQ;
+        mx[i] = sinks ? sinks[h] : -INFINITY;
+        dn[i] = sinks ? 1.f : 0.f;
+    }
+    for (int i = tid; i < TQ * H * dv; i += kThreads) acc[i] = 0.f;
+
+    for (int j0 = lo; j0 <= hi; j0 += TK) {
+        const int nk = min(TK, hi - j0 + 1);
+        __syncthreads();                                    // the tile before has been used up (and qs, mx, acc are set)
+        // (1) keys
+        for (int i = tid; i < nk * kw; i += kThreads) {
+            const int jj = i / kw, c = i - jj * kw, g = c / dk, d = c - g * dk;
+            const int pos = j0 + jj, lp = pos / page_size;
+            const int64_t page = table[lp];
+            kt[jj * kp + c] = page < 0 ? 0.f
+                                       : to_f32(kcache[((page * G + g) * page_size + (pos - lp * page_size)) * dk + d]);
+        }
+        __syncthreads();
+        // (2) raw scores of the query heads of one kv head, for one row and one key
+        for (int it = tid; it < G * nq * TK; it += kThreads) {
+            const int jj = it % TK, i = (it / TK) % nq, g = it / (TK * nq);
+            if (jj >= nk) continue;
+            const float* kr = kt + jj * kp + g * dk;
+            for (int u0 = 0; u0 < per; u0 += kMaxPer) {
+                float a[kMaxPer];
+#pragma unroll
+                for (int u = 0; u < kMaxPer; u++) a[u] = 0.f;
+                const float* qr = qs + (size_t)i * H * dk + (size_t)(g * per + u0) * dk;
+                const int nu = min(kMaxPer, per - u0);
+                for (int d = 0; d < dk; d++) {
+                    const float kv = kr[d];
+#pragma unroll
+                    for (int u = 0; u < kMaxPer; u++)
+                        if (u < nu) a[u] = fmaf(qr[u * dk + d], kv, a[u]);
+                }
+#pragma unroll
+                for (int u = 0; u < kMaxPer; u++)
+                    if (u < nu) raw[((g * per + u0 + u) * TQ + i) * TK + jj] = a[u];
+            }
+        }
+        __syncthreads();
+        // (3) values over the keys' place; mixing and mask
+        for (int i = tid; i < nk * vw; i += kThreads) {
+            const int jj = i / vw, c = i - jj * vw, g = c / dv, d = c - g * dv;
+            const int pos = j0 + jj, lp = pos / page_size;
+            const int64_t page = table[lp];
+            kt[jj * kp + c] = page < 0 ? 0.f
+                                       : to_f32(vcache[((page * G + g) * page_size + (pos - lp * page_size)) * dv + d]);
+        }
+        const int hb = (H + 3) / 4;
+        for (int it = tid; it < hb * nq * TK; it += kThreads) {
+            const int jj = it % TK, i = (it / TK) % nq, h0 = (it / (TK * nq)) * 4;
+            const int pos = j0 + jj, pi = p0 + i;
+            const bool visible = jj < nk && pos <= pi && (window <= 0 || pi - pos < window);
+            float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+            if (visible) {
+                const float* m0 = ms + h0 * H;
+                const bool b1 = h0 + 1 < H, b2 = h0 + 2 < H, b3 = h0 + 3 < H;
+                const float* m1 = b1 ? m0 + H : m0;
+                const float* m2 = b2 ? m0 + 2 * H : m0;
+                const float* m3 = b3 ? m0 + 3 * H : m0;
+                for (int g = 0; g < H; g++) {
+                    const float r = raw[(g * TQ + i) * TK + jj];
+                    a0 = fmaf(m0[g], r, a0);
+                    a1 = fmaf(m1[g], r, a1);
+                    a2 = fmaf(m2[g], r, a2);
+                    a3 = fmaf(m3[g], r, a3);
+                }
+            } else {
+                a0 = a1 = a2 = a3 = -INFINITY;
+            }
+            pr[((h0 + 0) * TQ + i) * TK + jj] = a0;
+            if (h0 + 1 < H) pr[((h0 + 1) * TQ + i) * TK + jj] = a1;
+            if (h0 + 2 < H) pr[((h0 + 2) * TQ + i) * TK + jj] = a2;
+            if (h0 + 3 < H) pr[((h0 + 3) * TQ + i) * TK + jj] = a3;
+        }
+        __syncthreads();
+        // (4) one warp per (head, row): maximum, weights, denominator (TK <= 32: a lane per key)
+        for (int rw = warp; rw < H * nq; rw += kThreads / 32) {
+            const int h = rw / nq, i = rw - h * nq;
+            float* row = pr + (h * TQ + i) * TK;
+            const float s = lane < TK ? row[lane] : -INFINITY;
+            const float m_old = mx[h * TQ + i];
+            const float m_new = fmaxf(m_old, warp_max(s));
+            const float w = (s == -INFINITY) ? 0.f : expf(s - m_new);       // m_new is finite whenever s is
+            const float c = (m_old == -INFINITY) ? 0.f : expf(m_old - m_new);
+            const float sum = warp_sum(w);
+            if (lane < TK) row[lane] = w;
+            if (lane == 0) {
+                mx[h * TQ + i] = m_new;
+                dn[h * TQ + i] = dn[h * TQ + i] * c + sum;
+                cr[h * TQ + i] = c;
+            }
+        }
+        __syncthreads();
+        // (5) output: a thread per (head, value channel), all rows of the tile
+        for (int it = tid; it < H * dv; it += kThreads) {
+            const int h = it / dv, e = it - h * dv;
+            const float* vr = kt + (h / per) * dv + e;
+            float a[kMaxTQ];
+#pragma unroll
+            for (int i = 0; i < kMaxTQ; i++) a[i] = 0.f;
+            for (int jj = 0; jj < nk; jj++) {
+                const float v = vr[jj * kp];
+#pragma unroll
+                for (int i = 0; i < kMaxTQ; i++)
+                    if (i < nq) a[i] = fmaf(pr[(h * TQ + i) * TK + jj], v, a[i]);
+            }
+#pragma unroll
+            for (int i = 0; i < kMaxTQ; i++)
+                if (i < nq) {
+                    float* o = acc + (size_t)i * H * dv + it;
+                    *o = *o * cr[h * TQ + i] + a[i];
+                }
+        }
+    }
+    __syncthreads();
+    for (int i = tid; i < nq * H * dv; i += kThreads) {
+        const int r = i / (H * dv), c = i - r * (H * dv), h = c / dv;
+        const float d = dn[h * TQ + r];
+        out[(int64_t)(row0 + r) * H * dv + c] = from_f32<T>(d > 0.f ? acc[i] / d : 0.f);
+    }
+}
+
+}  // namespace
+
+// out [n][H * dv] contiguous and q [n][H * dk] (row stride q_stride) in the element type `dtype`, which is also
+// the caches' ([pages][G][page_size][dk] and [pages][G][page_size][dv]); mix float32 [H][H]; sinks float32 [H]
+// or NULL; request s brings rows q_start[s] .. q_start[s + 1] at positions start_pos[s] ...; tile_rows: rows of a
+// query tile (1 for single tokens), n_tiles: an upper bound of the tiles (sum over requests of ceil(rows / tile_rows)).
+extern "C" int kllm_attention_mixed(void* out, const void* q, int64_t q_stride, const void* kcache, const void* vcache,
+                                    const float* mix, const float* sinks, const int* q_start, const int* start_pos,
+                                    const int* block_table, int max_blocks, int n_requests, int n_tiles, int tile_rows,
+                                    int n_heads, int n_kv, int dk, int dv, int page_size, int window, float scale,
+                                    int dtype, void* stream) {
+    if (n_requests <= 0 || n_tiles <= 0) return 0;
+    if (n_heads <= 0 || n_kv <= 0 || n_heads % n_kv || dk <= 0 || dv <= 0 || page_size <= 0)
+        KLLM_FAIL("mixed attention: %d heads on %d kv heads of sizes %d, %d", n_heads, n_kv, dk, dv);
+    if (tile_rows < 1 || tile_rows > kMaxTQ) KLLM_FAIL("mixed attention: tiles of %d rows (1 to %d)", tile_rows, kMaxTQ);
+    const size_t budget = 200 * 1024;
+    Shape sh = {n_heads, n_kv, dk, dv, tile_rows, 32};
+    while (sh.TK > 4 && smem_floats(sh) * sizeof(float) > budget) sh.TK /= 2;
+    while (sh.TQ > 1 && smem_floats(sh) * sizeof(float) > budget) sh.TQ /= 2;
+    if (sh.TQ != tile_rows) KLLM_FAIL("mixed attention: tiles of %d rows do not fit shared memory (%d would)", tile_rows, sh.TQ);
+    const size_t smem = smem_floats(sh) * sizeof(float);
+    if (smem > budget) KLLM_FAIL("mixed attention: %d heads of sizes %d, %d do not fit shared memory", n_heads, dk, dv);
+    cudaStream_t s = (cudaStream_t)stream;
+    static bool raised[2] = {false, false};
+    if (dtype == KLLM_F32) {
+        if (smem > 48 * 1024 && !raised[0]) {
+            cudaFuncSetAttribute(attention_mixed_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)budget);
+            raised[0] = true;
+        }
+        kllm_launch((attention_mixed_kernel<float>), dim3(n_tiles), dim3(kThreads), smem, s, (float*)out, (const float*)q,
+                    q_stride, (const float*)kcache, (const float*)vcache, mix, sinks, q_start, start_pos, block_table,
+                    max_blocks, n_requests, sh, page_size, window, scale);
+    } else if (dtype == KLLM_BF16) {
+        if (smem > 48 * 1024 && !raised[1]) {
+            cudaFuncSetAttribute(attention_mixed_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)budget);
+            raised[1] = true;
+        }
+        kllm_launch((attention_mixed_kernel<bf16>), dim3(n_tiles), dim3(kThreads), smem, s, (bf16*)out, (const bf16*)q,
+                    q_stride, (const bf16*)kcache, (const bf16*)vcache, mix, sinks, q_start, start_pos, block_table,
+                    max_blocks, n_requests, sh, page_size, window, scale);
+    } else {
+        KLLM_FAIL("mixed attention: unknown element type %d", dtype);
+    }
+    KLLM_LAUNCH_STATUS();
+}
+
+// The most rows a query tile of these sizes may have, at most 8: what fits shared memory beside a tile of 16
+// keys, or one row beside a smaller key tile; 0 when not even that fits.
+extern "C" int kllm_attention_mixed_tile_rows(int n_heads, int n_kv, int dk, int dv) {
+    if (n_heads <= 0 || n_kv <= 0 || dk <= 0 || dv <= 0) return 0;
+    Shape sh = {n_heads, n_kv, dk, dv, kMaxTQ, 16};
+    while (sh.TQ > 1 && smem_floats(sh) * sizeof(float) > 200 * 1024) sh.TQ /= 2;
+    while (sh.TK > 4 && smem_floats(sh) * sizeof(float) > 200 * 1024) sh.TK /= 2;
+    return smem_floats(sh) * sizeof(float) > 200 * 1024 ? 0 : sh.TQ;
+}

@@ -32,6 +32,30 @@ __global__ void embed_kernel(float* __restrict__ x, const T* __restrict__ table,
     for (int i = threadIdx.x; i < d; i += blockDim.x) xr[i] = to_f32(er[i]) * scale;
 }
 
+// out[t,j] = gelu_tanh(gate[t,j]) * E[ids[t], off + j] for j < width: a slice of a token's row of a second
+// table, gated by a projection of the residual stream (gelu_tanh(z) = 0.5 z (1 + tanh(sqrt(2 / pi) (z +
+// 0.044715 z^3)))).  gate float32 at its row stride, the product float32 before it is stored in out's
+// element type; ids as in embed_kernel.
+template <typename T>
+__global__ void gated_slice_kernel(T* __restrict__ out, const float* __restrict__ gate, int64_t gate_stride,
+                                   const T* __restrict__ table, int64_t table_stride, int off, int width,
+                                   const int* __restrict__ ids, const int* __restrict__ last_token, int vocab) {
+    griddep_wait();
+    griddep_launch();
+    const int t = blockIdx.x;
+    int id = ids[t];
+    if (id < 0 && last_token != nullptr) id = last_token[-id - 1];
+    T* orow = out + (int64_t)t * width;
+    const bool bad = id < 0 || id >= vocab;
+    const T* er = table + (bad ? 0 : (int64_t)id * table_stride) + off;
+    const float* gr = gate + (int64_t)t * gate_stride;
+    for (int j = threadIdx.x; j < width; j += blockDim.x) {
+        const float z = gr[j];
+        const float g = 0.5f * z * (1.f + tanhf(0.79788456080286536f * (z + 0.044715f * z * z * z)));
+        orow[j] = from_f32<T>(bad ? __int_as_float(0x7fc00000) : g * to_f32(er[j]));
+    }
+}
+
 // out[r,:] = in[rows[r],:] for rows of `width` elements of `elem` bytes each
 // (role of gather_rows_kernel, reference backend/model.cu:411-417).
 __global__ void gather_rows_kernel(char* __restrict__ out, const char* __restrict__ in,
@@ -64,6 +88,25 @@ extern "C" int kllm_embed(void* x, const void* table, const int* ids, const int*
         kllm_launch((embed_kernel<bf16>), dim3(n), dim3(threads), 0, s, (float*)x, (const bf16*)table, ids, last_token, d, vocab, scale);
     else
         KLLM_FAIL("embed: unknown element type %d", dtype);
+    KLLM_LAUNCH_STATUS();
+}
+
+// out [n][width] contiguous in the element type `dtype`, which is also the table's ([vocab][table_stride]).
+extern "C" int kllm_gated_slice(void* out, const float* gate, int64_t gate_stride, const void* table,
+                                int64_t table_stride, int off, int width, const int* ids, const int* last_token, int n,
+                                int vocab, int dtype, void* stream) {
+    if (n <= 0) return 0;
+    if (width <= 0 || off < 0 || off + width > table_stride) KLLM_FAIL("gated slice: columns [%d, %d) of %lld", off, off + width, (long long)table_stride);
+    cudaStream_t s = (cudaStream_t)stream;
+    const int threads = width >= 256 ? 256 : (width > 64 ? 128 : (width > 32 ? 64 : 32));
+    if (dtype == KLLM_F32)
+        kllm_launch((gated_slice_kernel<float>), dim3(n), dim3(threads), 0, s, (float*)out, gate, gate_stride,
+                    (const float*)table, table_stride, off, width, ids, last_token, vocab);
+    else if (dtype == KLLM_BF16)
+        kllm_launch((gated_slice_kernel<bf16>), dim3(n), dim3(threads), 0, s, (bf16*)out, gate, gate_stride,
+                    (const bf16*)table, table_stride, off, width, ids, last_token, vocab);
+    else
+        KLLM_FAIL("gated slice: unknown element type %d", dtype);
     KLLM_LAUNCH_STATUS();
 }
 

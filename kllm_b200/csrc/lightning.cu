@@ -1,0 +1,190 @@
+// Linear attention with one fixed decay per head ("lightning attention"), for mixed batches of
+// prompt portions and single tokens, with the state of every request in a slot of a state tensor.
+//
+// Per head, with dk key channels, dv value channels, a decay w in (0, 1] and a state S [dk][dv]
+// that starts at zero for a new request:
+//
+//     q, k, v = silu of the head's parts of the projections
+//     S_t = w S_(t-1) + k_t v_t^T            o_t = S_t^T q_t
+//
+// Everything is float32: the projections arrive unrounded, the activation, the powers of the
+// decay, the state and the sums.  A request's rows are taken in chunks of up to C rows; inside a
+// chunk that starts with the state S,
+//
+//     o_i = w^(i+1) S^T q_i + sum over j <= i of w^(i-j) (q_i . k_j) v_j
+//     S'  = w^n S + sum over j of w^(n-1-j) k_j v_j^T                          (n rows in the chunk)
+//
+// which is the recurrence written out, so a prompt cut anywhere gives the same sums up to their
+// order.  A CTA takes (head, slice of value channels, request): it keeps its [dk][slice] part of
+// the state in shared memory from the first chunk to the last and writes it back to the slot.
+// A single decoded token is a chunk of one row.
+//
+// The second kernel joins the heads: y = o / rms(o over ALL heads' values) * gain * sigmoid(g).
+#include "common.cuh"
+
+KLLM_EXPORT_LAST_ERROR(lightning)
+
+namespace {
+
+constexpr int kChunk = 32;
+constexpr int kThreads = 256;
+
+__device__ __forceinline__ float silu_f(float z) { return z / (1.f + expf(-z)); }
+
+// grid (heads * slices, requests).  Shared memory: S [dk][sl], q [C][dk + 1], k [C][dk + 1], v [C][sl],
+// A [C][C + 1], pw [C + 1].
+__global__ void __launch_bounds__(kThreads)
+lightning_scan_kernel(float* __restrict__ o, int64_t o_stride, const float* __restrict__ q, int64_t q_stride,
+                      const float* __restrict__ k, int64_t k_stride, const float* __restrict__ v, int64_t v_stride,
+                      const float* __restrict__ decay, float* __restrict__ state, int64_t state_stride,
+                      const int* __restrict__ q_start, const int* __restrict__ state_slots, int heads, int dk, int dv,
+                      int sl, int slices) {
+    extern __shared__ float sm[];
+    const int head = blockIdx.x / slices, slice = blockIdx.x - head * slices;
+    const int e0 = slice * sl, ne = min(sl, dv - e0);
+    const int req = blockIdx.y;
+    const int qp = dk + 1;
+    float* S = sm;                          // [dk][sl]
+    float* qs = S + dk * sl;                // [C][dk + 1]
+    float* ks = qs + kChunk * qp;           // [C][dk + 1]
+    float* vs = ks + kChunk * qp;           // [C][sl]
+    float* A = vs + kChunk * sl;            // [C][C + 1]
+    float* pw = A + kChunk * (kChunk + 1);  // [C + 1]: w^0 .. w^C
+    const int tid = threadIdx.x;
+    const float w = decay[head];
+    if (tid <= kChunk) pw[tid] = (float)pow((double)w, (double)tid);
+    griddep_wait();
+    griddep_launch();
+    const int row0 = q_start[req], row1 = q_start[req + 1];
+    float* slot = state + (int64_t)state_slots[req] * state_stride + (int64_t)head * dk * dv;
+    for (int i = tid; i < dk * ne; i += kThreads) {
+        const int d = i / ne, e = i - d * ne;
+        S[d * sl + e] = slot[(int64_t)d * dv + e0 + e];
+    }
+    for (int c0 = row0; c0 < row1; c0 += kChunk) {
+        const int n = min(kChunk, row1 - c0);
+        __syncthreads();                    // the chunk before has been used up; S and pw are written
+        for (int i = tid; i < n * dk; i += kThreads) {
+            const int r = i / dk, d = i - r * dk;
+            qs[r * qp + d] = silu_f(q[(int64_t)(c0 + r) * q_stride + head * dk + d]);
+            ks[r * qp + d] = silu_f(k[(int64_t)(c0 + r) * k_stride + head * dk + d]);
+        }
+        for (int i = tid; i < n * ne; i += kThreads) {
+            const int r = i / ne, e = i - r * ne;
+            vs[r * sl + e] = silu_f(v[(int64_t)(c0 + r) * v_stride + head * dv + e0 + e]);
+        }
+        __syncthreads();
+        // A[i][j] = w^(i-j) q_i . k_j for j <= i
+        for (int it = tid; it < n * n; it += kThreads) {
+            const int i = it / n, j = it - i * n;
+            float a = 0.f;
+            if (j <= i) {
+                const float* qi = qs + i * qp;
+                const float* kj = ks + j * qp;
+                for (int d = 0; d < dk; d++) a = fmaf(qi[d], kj[d], a);
+                a *= pw[i - j];
+            }
+            A[i * (kChunk + 1) + j] = a;
+        }
+        __syncthreads();
+        // o_i[e] = w^(i+1) sum_d S[d][e] q_i[d] + sum_{j<=i} A[i][j] v_j[e]
+        for (int it = tid; it < n * ne; it += kThreads) {
+            const int i = it / ne, e = it - i * ne;
+            const float* qi = qs + i * qp;
+            float acc = 0.f;
+            for (int d = 0; d < dk; d++) acc = fmaf(S[d * sl + e], qi[d], acc);
+            acc *= pw[i + 1];
+            const float* Ai = A + i * (kChunk + 1);
+            for (int j = 0; j <= i; j++) acc = fmaf(Ai[j], vs[j * sl + e], acc);
+            o[(int64_t)(c0 + i) * o_stride + head * dv + e0 + e] = acc;
+        }
+        __syncthreads();
+        // S[d][e] = w^n S[d][e] + sum_j w^(n-1-j) k_j[d] v_j[e]
+        for (int it = tid; it < dk * ne; it += kThreads) {
+            const int d = it / ne, e = it - d * ne;
+            float acc = S[d * sl + e] * pw[n];
+            for (int j = 0; j < n; j++) acc = fmaf(ks[j * qp + d] * pw[n - 1 - j], vs[j * sl + e], acc);
+            S[d * sl + e] = acc;
+        }
+    }
+    __syncthreads();
+    for (int i = tid; i < dk * ne; i += kThreads) {
+        const int d = i / ne, e = i - d * ne;
+        slot[(int64_t)d * dv + e0 + e] = S[d * sl + e];
+    }
+}
+
+// y[t,:] = o[t,:] * rsqrt(mean over all `width` values of o[t,:]^2 + eps) * gain * sigmoid(g[t,:]); one CTA per row.
+template <typename T>
+__global__ void __launch_bounds__(kThreads)
+gate_norm_kernel(T* __restrict__ y, const float* __restrict__ o, int64_t o_stride, const float* __restrict__ g,
+                 int64_t g_stride, const float* __restrict__ gain, int width, float eps) {
+    __shared__ float red[32];
+    griddep_wait();
+    griddep_launch();
+    const int t = blockIdx.x;
+    const float* orow = o + (int64_t)t * o_stride;
+    const float* grow = g + (int64_t)t * g_stride;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < width; i += kThreads) ss += orow[i] * orow[i];
+    ss = block_sum(ss, red);
+    const float scale = rsqrtf(ss / (float)width + eps);
+    T* yr = y + (int64_t)t * width;
+    for (int i = threadIdx.x; i < width; i += kThreads)
+        yr[i] = from_f32<T>(orow[i] * scale * gain[i] / (1.f + expf(-grow[i])));
+}
+
+size_t scan_smem(int dk, int sl) {
+    return sizeof(float) * ((size_t)dk * sl + 2 * (size_t)kChunk * (dk + 1) + (size_t)kChunk * sl +
+                            (size_t)kChunk * (kChunk + 1) + kChunk + 1);
+}
+
+}  // namespace
+
+// o float32 [n][heads * dv]; q, k float32 rows of heads * dk, v float32 rows of heads * dv (the projections,
+// before their activation), each at its row stride; decay float32 [heads]; state float32 [slots][state_stride]
+// whose first heads * dk * dv values are S as [heads][dk][dv]; q_start int32 [requests + 1], state_slots int32
+// [requests].
+extern "C" int kllm_lightning_scan(float* o, int64_t o_stride, const float* q, int64_t q_stride, const float* k,
+                                   int64_t k_stride, const float* v, int64_t v_stride, const float* decay, float* state,
+                                   int64_t state_stride, const int* q_start, const int* state_slots, int n,
+                                   int n_requests, int heads, int dk, int dv, void* stream) {
+    if (n <= 0 || n_requests <= 0) return 0;
+    if (heads <= 0 || dk <= 0 || dv <= 0) KLLM_FAIL("lightning scan: %d heads of sizes %d, %d", heads, dk, dv);
+    if (n_requests > 65535) KLLM_FAIL("lightning scan: %d requests in one launch", n_requests);
+    if (state_stride < (int64_t)heads * dk * dv) KLLM_FAIL("lightning scan: a state slot of %lld values is too small", (long long)state_stride);
+    // the slice of value channels: as wide as the shared memory of a CTA holds beside the chunk, at most 64
+    int sl = dv < 64 ? dv : 64;
+    while (sl > 1 && scan_smem(dk, sl) > 200 * 1024) sl = (sl + 1) / 2;
+    if (scan_smem(dk, sl) > 200 * 1024) KLLM_FAIL("lightning scan: a head of %d key channels does not fit shared memory", dk);
+    const int slices = (dv + sl - 1) / sl;
+    const size_t smem = scan_smem(dk, sl);
+    static size_t allowed = 48 * 1024;
+    if (smem > allowed) {
+        cudaError_t e = cudaFuncSetAttribute(lightning_scan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        if (e != cudaSuccess) KLLM_FAIL("lightning scan: %s", cudaGetErrorString(e));
+        allowed = 200 * 1024;
+    }
+    kllm_launch((lightning_scan_kernel), dim3(heads * slices, n_requests), dim3(kThreads), smem, (cudaStream_t)stream, o,
+                o_stride, q, q_stride, k, k_stride, v, v_stride, decay, state, state_stride, q_start, state_slots, heads,
+                dk, dv, sl, slices);
+    KLLM_LAUNCH_STATUS();
+}
+
+// y [n][width] contiguous in the element type `dtype`; o, g float32 rows of `width` values at their strides;
+// gain float32 [width].
+extern "C" int kllm_lightning_gate_norm(void* y, const float* o, int64_t o_stride, const float* g, int64_t g_stride,
+                                        const float* gain, int n, int width, float eps, int dtype, void* stream) {
+    if (n <= 0) return 0;
+    if (width <= 0) KLLM_FAIL("lightning gate norm: width %d", width);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == KLLM_F32)
+        kllm_launch((gate_norm_kernel<float>), dim3(n), dim3(kThreads), 0, s, (float*)y, o, o_stride, g, g_stride, gain,
+                    width, eps);
+    else if (dtype == KLLM_BF16)
+        kllm_launch((gate_norm_kernel<bf16>), dim3(n), dim3(kThreads), 0, s, (bf16*)y, o, o_stride, g, g_stride, gain,
+                    width, eps);
+    else
+        KLLM_FAIL("lightning gate norm: unknown element type %d", dtype);
+    KLLM_LAUNCH_STATUS();
+}

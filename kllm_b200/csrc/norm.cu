@@ -188,9 +188,14 @@ rmsnorm_add_kernel(float* __restrict__ x, const float* __restrict__ y, const flo
         s2 += v * v;
     }
     if (out == nullptr) return;
+    T* orow = out + (int64_t)r * d;
+    if (gain2 == nullptr) {
+        // no norm in front of the next sublayer: it reads the updated rows themselves, in its element type
+        for (int i = threadIdx.x; i < d; i += blockDim.x) orow[i] = from_f32<T>(xr[i]);
+        return;
+    }
     s2 = block_sum(s2, red);
     const float scale2 = rsqrtf(s2 / (float)d + eps2);
-    T* orow = out + (int64_t)r * d;
     for (int i = threadIdx.x; i < d; i += blockDim.x) orow[i] = from_f32<T>(xr[i] * scale2 * gain2[i]);
 }
 
@@ -311,12 +316,11 @@ add_layernorm_vec4_kernel(float* __restrict__ x, const float* __restrict__ res, 
 }  // namespace
 
 // x float32 [n][d] (updated), y float32 [n][d], gain float32 [d]; out (optional, element type
-// `dtype`) [n][d] with gain2 [d].
+// `dtype`) [n][d] with gain2 [d]; gain2 NULL: out gets the updated rows as they are, in its element type.
 extern "C" int kllm_rmsnorm_add(void* x, const void* y, const void* gain, float eps, void* out, const void* gain2,
                                 float eps2, int n_rows, int d, int dtype, void* stream) {
     if (n_rows <= 0) return 0;
     if (d <= 0) KLLM_FAIL("rmsnorm_add: width %d must be positive", d);
-    if (out && !gain2) KLLM_FAIL("rmsnorm_add: a second norm needs its gain");
     cudaStream_t s = (cudaStream_t)stream;
     const int threads = d <= 512 ? 64 : (d <= 2048 ? 128 : kThreads);
     if (dtype == KLLM_F32)

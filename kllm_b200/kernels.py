@@ -61,6 +61,11 @@ def _i32(t: Optional[torch.Tensor], what: str):
         raise KernelError(f"{what} must be a contiguous int32 tensor")
 
 
+def _f64(t: Optional[torch.Tensor], what: str):
+    if t is not None and (t.dtype != torch.float64 or not t.is_contiguous()):
+        raise KernelError(f"{what} must be a contiguous float64 tensor")
+
+
 def embed(out_x: torch.Tensor, table: torch.Tensor, ids: torch.Tensor,
           last_token: Optional[torch.Tensor] = None, scale: float = 1.0) -> None:
     """out_x[t,:] = float32(table[ids[t],:]) * scale; out_x float32 [n, d].  With ``last_token``
@@ -89,6 +94,25 @@ def gather_rows(out: torch.Tensor, src: torch.Tensor, rows: torch.Tensor) -> Non
     rc = lib.kllm_gather_rows(_p(out), _p(src), _p(rows), rows.numel(),
                               ctypes.c_int64(src.shape[1] * src.element_size()), _stream())
     _check(lib, "embedding", rc)
+
+
+def gated_slice(gate: torch.Tensor, table: torch.Tensor, offset: int, ids: torch.Tensor,
+                last_token: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """[n, P] in the table's dtype: gelu_tanh(gate[t, j]) * table[ids[t], offset + j], ``gate`` float32 [n, P]
+    with dense rows, ``table`` contiguous [vocab, columns]: a slice of each token's row of a second embedding
+    table, gated (csrc/embedding.cu).  Ids as in ``embed``."""
+    _cuda(gate, table, ids, last_token)
+    _i32(ids, "ids"); _i32(last_token, "last_token")
+    n, P = gate.shape
+    if gate.dtype != torch.float32 or gate.stride(1) != 1 or not table.is_contiguous() or ids.numel() != n \
+            or offset < 0 or offset + P > table.shape[1]:
+        raise KernelError("gated_slice: gate float32 [n, P] with dense rows, table contiguous with columns offset .. offset + P")
+    out = torch.empty((n, P), dtype=table.dtype, device=gate.device)
+    lib = load_library("embedding")
+    rc = lib.kllm_gated_slice(_p(out), _p(gate), ctypes.c_int64(gate.stride(0)), _p(table), ctypes.c_int64(table.shape[1]),
+                              int(offset), P, _p(ids), _p(last_token), n, table.shape[0], dtype_code(table.dtype), _stream())
+    _check(lib, "embedding", rc)
+    return out
 
 
 def add_rmsnorm(x: torch.Tensor, res: Optional[torch.Tensor], out: torch.Tensor, gain: torch.Tensor,
@@ -146,7 +170,9 @@ def rmsnorm_add(x: torch.Tensor, y: torch.Tensor, gain: torch.Tensor, eps: float
                 out: Optional[torch.Tensor] = None, gain2: Optional[torch.Tensor] = None, eps2: float = 0.0) -> None:
     """x += rmsnorm(y) * gain, all float32 [n, d]: a norm on a sublayer's output as it joins
     the residual stream.  With ``out`` [n, d] (model dtype) and ``gain2`` also
-    out = rmsnorm(x) * gain2 of the updated rows, the norm in front of the next sublayer."""
+    out = rmsnorm(x) * gain2 of the updated rows, the norm in front of the next sublayer; with
+    ``out`` alone the updated rows themselves in out's dtype (a next sublayer that reads the
+    stream as it is)."""
     _cuda(x, y, gain, out, gain2)
     d = x.shape[1]
     for t in (x, y):
@@ -154,9 +180,9 @@ def rmsnorm_add(x: torch.Tensor, y: torch.Tensor, gain: torch.Tensor, eps: float
             raise KernelError("rmsnorm_add: x and y must be contiguous float32 of one shape")
     if gain.dtype != torch.float32 or gain.numel() != d:
         raise KernelError("rmsnorm_add: gain must be float32 [d]")
-    if out is not None and (gain2 is None or gain2.dtype != torch.float32 or gain2.numel() != d
-                            or not out.is_contiguous() or out.shape != x.shape):
-        raise KernelError("rmsnorm_add: the second norm needs a float32 gain [d] and a contiguous out like x")
+    if out is not None and (not out.is_contiguous() or out.shape != x.shape or (
+            gain2 is not None and (gain2.dtype != torch.float32 or gain2.numel() != d))):
+        raise KernelError("rmsnorm_add: out contiguous like x, a second norm's gain float32 [d]")
     lib = load_library("norm")
     rc = lib.kllm_rmsnorm_add(_p(x), _p(y), _p(gain), ctypes.c_float(eps), _p(out), _p(gain2), ctypes.c_float(eps2),
                               x.shape[0], d, dtype_code(out.dtype if out is not None else torch.float32), _stream())
@@ -166,14 +192,19 @@ def rmsnorm_add(x: torch.Tensor, y: torch.Tensor, gain: torch.Tensor, eps: float
 def qknorm_append(q_out: torch.Tensor, qkv: torch.Tensor, q_gain: torch.Tensor, k_gain: Optional[torch.Tensor],
                   eps: float, temp_coef: float, temp_every: int, positions: torch.Tensor, token_req: torch.Tensor,
                   block_table: Optional[torch.Tensor], kcache: Optional[torch.Tensor], vcache: Optional[torch.Tensor],
-                  n_heads: int, n_kv: int, head_dim: int, v_head_dim: int) -> None:
+                  n_heads: int, n_kv: int, head_dim: int, v_head_dim: int, rot: int = 0,
+                  freq: Optional[torch.Tensor] = None) -> None:
     """RMS norm of the whole query projection and of the whole key projection (float32
     ``qkv`` [n, H*dk + G*dk + G*dv]), the queries' temperature 1 + coef * ln(floor((p + 1) /
-    every) + 1), q stored in ``q_out`` [n, H*dk] (model dtype) and k, v written to the paged
+    every) + 1), then with ``rot`` > 0 the rotation of the first ``rot`` values of every query and
+    key head (pair (i, i + rot / 2) turns by position * freq[i]; ``freq`` float64 [rot / 2]), q stored
+    in ``q_out`` [n, H*dk] (model dtype) and k, v written to the paged
     caches [pages, G, page_size, dk] / [pages, G, page_size, dv] (csrc/qknorm_append.cu).
     With ``kcache`` None ``qkv`` holds queries only and nothing is stored."""
-    _cuda(q_out, qkv, q_gain, k_gain, positions, token_req, block_table, kcache, vcache)
-    _i32(positions, "positions"); _i32(token_req, "token_req"); _i32(block_table, "block_table")
+    _cuda(q_out, qkv, q_gain, k_gain, positions, token_req, block_table, kcache, vcache, freq)
+    _i32(positions, "positions"); _i32(token_req, "token_req"); _i32(block_table, "block_table"); _f64(freq, "freq")
+    if rot and (freq is None or freq.numel() != rot // 2 or rot % 2 or rot > head_dim):
+        raise KernelError("qknorm_append: an even rotary width within the head, one frequency per rotated pair")
     n = qkv.shape[0]
     Q, K, V = n_heads * head_dim, n_kv * head_dim, n_kv * v_head_dim
     if qkv.dtype != torch.float32 or qkv.stride(1) != 1 or qkv.shape[1] != (Q + K + V if kcache is not None else Q):
@@ -195,7 +226,8 @@ def qknorm_append(q_out: torch.Tensor, qkv: torch.Tensor, q_gain: torch.Tensor, 
     rc = lib.kllm_qknorm_append(_p(q_out), _p(qkv), ctypes.c_int64(qkv.stride(0)), _p(q_gain), _p(k_gain),
                                 ctypes.c_float(eps), ctypes.c_float(temp_coef), int(temp_every or 1), _p(positions),
                                 _p(token_req), _p(block_table), max_blocks, _p(kcache), _p(vcache), n, n_heads, n_kv,
-                                head_dim, v_head_dim, page_size, dtype_code(q_out.dtype), _stream())
+                                head_dim, v_head_dim, page_size, int(rot or 0), _p(freq if rot else None),
+                                dtype_code(q_out.dtype), _stream())
     _check(lib, "qknorm_append", rc)
 
 
@@ -227,11 +259,6 @@ def latent_norm_append(q_out: torch.Tensor, proj: torch.Tensor, q_gain: torch.Te
     _check(lib, "latent", rc)
 
 
-def _f64(t: Optional[torch.Tensor], what: str):
-    if t is not None and (t.dtype != torch.float64 or not t.is_contiguous()):
-        raise KernelError(f"{what} must be a contiguous float64 tensor")
-
-
 def latent_rope_append(q_plain: torch.Tensor, q_full: torch.Tensor, proj: torch.Tensor, kv_gain: Optional[torch.Tensor],
                        eps: float, freq: Optional[torch.Tensor], amplitude: float, positions: torch.Tensor,
                        token_req: torch.Tensor, block_table: Optional[torch.Tensor], cache: Optional[torch.Tensor],
@@ -247,8 +274,10 @@ def latent_rope_append(q_plain: torch.Tensor, q_full: torch.Tensor, proj: torch.
     _cuda(q_plain, q_full, proj, kv_gain, freq, positions, token_req, block_table, cache)
     _i32(positions, "positions"); _i32(token_req, "token_req"); _i32(block_table, "block_table"); _f64(freq, "freq")
     n = proj.shape[0]
-    if proj.dtype != torch.float32 or proj.stride(1) != 1 or proj.shape[1] < n_heads * (dk + dr) + rank + dr:
-        raise KernelError("latent_rope_append: the projections must be float32 [n, >= H (dk + dr) + R + dr] with dense rows")
+    if proj.dtype != torch.float32 or proj.stride(1) != 1 or \
+            proj.shape[1] < n_heads * (dk + dr) + (rank + dr if cache is not None else 0):
+        raise KernelError("latent_rope_append: the projections must be float32 [n, >= H (dk + dr) (+ R + dr with a store)] "
+                          "with dense rows")
     if (tuple(q_plain.shape) != (n, n_heads * dk) or tuple(q_full.shape) != (n, n_heads * (rank + dr))
             or not q_plain.is_contiguous() or not q_full.is_contiguous() or q_plain.dtype != q_full.dtype):
         raise KernelError("latent_rope_append: q_plain [n, H dk] and q_full [n, H (R + dr)] contiguous, of one dtype")
@@ -1359,21 +1388,110 @@ def wkv_gate_norm(o: torch.Tensor, g: torch.Tensor, gain: torch.Tensor, eps: flo
     return y
 
 
-_UNARY = {"relu2": 0, "tanh": 1}
+_UNARY = {"relu2": 0, "tanh": 1, "copy": 2, "gelu": 3, "gelu_tanh": 4, "softcap": 5}
 
 
-def unary(x: torch.Tensor, op: str, dtype: torch.dtype) -> torch.Tensor:
+def unary(x: torch.Tensor, op: str, dtype: torch.dtype, arg: float = 0.0, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """f(x) elementwise of a float32 matrix with dense rows, stored in ``dtype``; ``op``:
-    "relu2" (the square of relu) or "tanh"."""
-    _cuda(x)
+    "relu2" (the square of relu), "tanh", "copy" (the value itself: a change of dtype), "gelu" (with the
+    error function), "gelu_tanh" (its tanh form) or "softcap" (arg * tanh(x / arg)).  ``out``: where to
+    store (x itself for a float32 result in place)."""
+    _cuda(x, out)
     if x.dtype != torch.float32 or x.dim() != 2 or x.stride(1) != 1:
         raise KernelError("unary: the input must be a float32 matrix with dense rows")
-    out = torch.empty(x.shape, dtype=dtype, device=x.device)
+    if out is None:
+        out = torch.empty(x.shape, dtype=dtype, device=x.device)
+    elif out.dtype != dtype or out.shape != x.shape or out.stride(1) != 1:
+        raise KernelError("unary: out must have x's shape, dense rows and the named dtype")
     lib = load_library("activation")
     rc = lib.kllm_unary(_p(out), ctypes.c_int64(out.stride(0)), _p(x), ctypes.c_int64(x.stride(0)), x.shape[0],
-                        x.shape[1], _UNARY[op], dtype_code(dtype), _stream())
+                        x.shape[1], _UNARY[op], ctypes.c_float(arg), dtype_code(dtype), _stream())
     _check(lib, "activation", rc)
     return out
+
+
+# ---- linear attention with a fixed decay per head (csrc/lightning.cu) -------------------
+
+def lightning_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, decay: torch.Tensor, state: torch.Tensor, ctx,
+                   heads: int, dk: int, dv: int) -> torch.Tensor:
+    """o float32 [n, heads * dv] of the recurrence S_t = decay_h S_(t-1) + k_t v_t^T, o_t = S_t^T q_t per head, with
+    q, k, v = silu of the float32 projections given here (rows of heads * dk, heads * dk, heads * dv values, dense,
+    at their own row strides); ``state`` float32 [slots, >= heads * dk * dv] holds S as [heads, dk, dv] per
+    request slot and is carried on; every request's rows are taken in order."""
+    _cuda(q, k, v, decay, state)
+    _f32_rows(q, heads * dk, "lightning_scan: q"); _f32_rows(k, heads * dk, "lightning_scan: k")
+    _f32_rows(v, heads * dv, "lightning_scan: v")
+    if decay.dtype != torch.float32 or decay.numel() != heads or not decay.is_contiguous():
+        raise KernelError("lightning_scan: one float32 decay per head")
+    if state.dtype != torch.float32 or state.dim() != 2 or state.stride(1) != 1 or state.shape[1] < heads * dk * dv:
+        raise KernelError("lightning_scan: the state must be float32 [slots, >= heads * dk * dv]")
+    _i32(ctx.q_start, "q_start"); _i32(ctx.state_slots, "state_slots")
+    o = torch.empty((q.shape[0], heads * dv), dtype=torch.float32, device=q.device)
+    lib = load_library("lightning")
+    rc = lib.kllm_lightning_scan(_p(o), ctypes.c_int64(o.stride(0)), _p(q), ctypes.c_int64(q.stride(0)), _p(k),
+                                 ctypes.c_int64(k.stride(0)), _p(v), ctypes.c_int64(v.stride(0)), _p(decay), _p(state),
+                                 ctypes.c_int64(state.stride(0)), _p(ctx.q_start), _p(ctx.state_slots), q.shape[0],
+                                 ctx.n_requests, heads, dk, dv, _stream())
+    _check(lib, "lightning", rc)
+    return o
+
+
+def lightning_gate_norm(o: torch.Tensor, g: torch.Tensor, gain: torch.Tensor, eps: float, dtype: torch.dtype) -> torch.Tensor:
+    """y = o / rms(o over the whole row) * gain * sigmoid(g), stored in ``dtype``; o, g float32 [n, width] with dense rows."""
+    _cuda(o, g, gain)
+    width = o.shape[1]
+    _f32_rows(o, width, "lightning_gate_norm: o"); _f32_rows(g, width, "lightning_gate_norm: g")
+    if gain.dtype != torch.float32 or gain.numel() != width or not gain.is_contiguous() or g.shape[0] != o.shape[0]:
+        raise KernelError("lightning_gate_norm: gain must be contiguous float32 [width], g as many rows as o")
+    y = torch.empty((o.shape[0], width), dtype=dtype, device=o.device)
+    lib = load_library("lightning")
+    rc = lib.kllm_lightning_gate_norm(_p(y), _p(o), ctypes.c_int64(o.stride(0)), _p(g), ctypes.c_int64(g.stride(0)),
+                                      _p(gain), o.shape[0], width, ctypes.c_float(eps), dtype_code(dtype), _stream())
+    _check(lib, "lightning", rc)
+    return y
+
+
+# ---- attention with scores mixed across the heads (csrc/attention_mixed.cu) ---------------
+
+_mixed_tile_rows = {}
+
+
+def attention_mixed(out: torch.Tensor, q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, mix: torch.Tensor,
+                    ctx, block_table: torch.Tensor, n_heads: int, n_kv: int, head_dim: int, v_head_dim: int,
+                    window: int, scale: float, sinks: Optional[torch.Tensor] = None) -> None:
+    """Causal grouped attention of the step's tokens over the paged cache whose scaled scores are mixed across the
+    heads before mask and softmax: s_h = sum_g mix[h, g] * scale * q_g . k_kv(g); ``mix`` float32 [H, H]; ``window``
+    W > 0: a query sees the last W keys, its own included; ``sinks`` (float32 [H]): exp(sinks[h]) joins the
+    denominator of head h.  Scores, mixing, weights and sums are float32 in both dtypes.  Single tokens run as tiles
+    of one row, portions as tiles of up to eight rows of one request."""
+    _cuda(out, q, kcache, vcache, mix, block_table, sinks)
+    _i32(block_table, "block_table"); _i32(ctx.q_start, "q_start"); _i32(ctx.start_pos, "start_pos")
+    _slopes_arg(sinks, n_heads, "sinks")
+    n = q.shape[0]
+    if (q.stride(1) != 1 or q.shape[1] != n_heads * head_dim or not out.is_contiguous() or out.dtype != q.dtype
+            or tuple(out.shape) != (n, n_heads * v_head_dim) or kcache.dtype != q.dtype or vcache.dtype != q.dtype):
+        raise KernelError("attention_mixed: q [n, H dk] with dense rows, out contiguous [n, H dv], one dtype with the caches")
+    page_size = kcache.shape[2]
+    if (not kcache.is_contiguous() or not vcache.is_contiguous() or tuple(kcache.shape[1:]) != (n_kv, page_size, head_dim)
+            or tuple(vcache.shape) != (kcache.shape[0], n_kv, page_size, v_head_dim)):
+        raise KernelError("attention_mixed: caches [pages, kv heads, page_size, size]")
+    if mix.dtype != torch.float32 or not mix.is_contiguous() or tuple(mix.shape) != (n_heads, n_heads):
+        raise KernelError("attention_mixed: the mixing matrix must be contiguous float32 [heads, heads]")
+    lib = load_library("attention_mixed")
+    key = (n_heads, n_kv, head_dim, v_head_dim)
+    if key not in _mixed_tile_rows:
+        _mixed_tile_rows[key] = int(lib.kllm_attention_mixed_tile_rows(*key))
+    rows = _mixed_tile_rows[key]
+    if rows <= 0:
+        raise KernelError(f"attention_mixed: {n_heads} heads of sizes {head_dim}, {v_head_dim} do not fit a CTA's shared memory")
+    if ctx.all_single:
+        rows = 1
+    tiles = ctx.n_requests if rows == 1 else ctx.n_tokens // rows + ctx.n_requests
+    rc = lib.kllm_attention_mixed(_p(out), _p(q), ctypes.c_int64(q.stride(0)), _p(kcache), _p(vcache), _p(mix), _p(sinks),
+                                  _p(ctx.q_start), _p(ctx.start_pos), _p(block_table), block_table.shape[1],
+                                  ctx.n_requests, int(tiles), int(rows), n_heads, n_kv, head_dim, v_head_dim, page_size,
+                                  int(window or 0), ctypes.c_float(scale), dtype_code(q.dtype), _stream())
+    _check(lib, "attention_mixed", rc)
 
 
 # ---- routed experts (csrc/moe.cu) ------------------------------------------------------

@@ -1,3 +1,3 @@
 """Architectures.  Importing this package registers each of them by the name that
 stands in ``architectures`` of config.json."""
-from . import llama, nutizen, ronurax, sozarax  # noqa: F401
+from . import llama, nutizen, ronurax, senulix, sozarax  # noqa: F401

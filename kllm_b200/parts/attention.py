@@ -32,6 +32,12 @@ a1 - lambda a2, divided by its root mean square over the head's values (eps insi
 multiplied by 1 - diff.  The two maps run as 2H query heads over 2G key heads and G value heads,
 the queries' rows reordered when the weights are bound so that the heads of a key head are
 neighbours; the maps' outputs stay float32 until they are combined).
+``score_mix`` (the full name of a float32 tensor M [H, H]: the heads' scaled scores are mixed before mask and
+softmax, s_h = sum_g M[h, g] * scale * q_g . k_kv(g); such a layer runs a kernel of its own, csrc/attention_mixed.cu,
+which holds all heads of a tile of rows in one CTA, and needs a ``qk_transform`` with ``prepare``),
+``sink`` ("zero": a term exp(0) = 1 joins every head's softmax denominator, a sink without key, value or tensor;
+or the full name of a float32 tensor [H] of learned sink scores; taken by the mixed kernel and by the kernels
+that take ``sinks``).
 Tensors: ``<prefix>.{q,k,v,o}_proj.weight`` with shapes [H*hd, d], [G*hd, d],
 [G*vd, d], [d, H*vd]; no bias (reference backend/model.cu:1090-1104).  At bind time
 q, k and v are stacked into one [(H+2G)*hd, d] matrix so the three projections are
@@ -97,6 +103,17 @@ class PagedAttention:
                              "projections (prepare)")
         self.bias = None
         self.lam = 0.0
+        self.mix_name = p.get("score_mix")
+        self.mix = None
+        self.sink_name = p.get("sink")
+        self.sinks = None
+        if self.sink_name == "zero":
+            self.sinks = torch.zeros(self.n_heads, dtype=torch.float32, device=env.device)
+        if self.mix_name and (not self._prepares or self.differential or self.segment or p.get("score_slopes")):
+            raise ValueError("attention: mixed scores need a qk_transform that stores keys and values (prepare) and go "
+                             "without differential maps, segments and score slopes")
+        if self.sink_name and not self._prepares:
+            raise ValueError("attention: a sink needs a qk_transform that stores keys and values (prepare)")
         slopes = p.get("score_slopes")
         if slopes == "geometric":
             # the slopes 2^(-8 (h + 1) / H) of a bias that grows with the distance, head by head
@@ -133,6 +150,10 @@ class PagedAttention:
         if self.differential:
             out += [TensorSpec(self.differential["tensors"][k], (self.head_dim,), store="float32", init="normal")
                     for k in ("lq1", "lk1", "lq2", "lk2")]
+        if self.mix_name:
+            out.append(TensorSpec(self.mix_name, (self.n_heads, self.n_heads), store="float32", init="eye"))
+        if self.sink_name and self.sink_name != "zero":
+            out.append(TensorSpec(self.sink_name, (self.n_heads,), store="float32", init="zeros"))
         return out + (self.position.tensor_specs() if self.position else []) + \
             (self.qk_transform.tensor_specs() if self.qk_transform else [])
 
@@ -158,6 +179,10 @@ class PagedAttention:
             v = {k: tensors[self.differential["tensors"][k]].double() for k in ("lq1", "lk1", "lq2", "lk2")}
             self.lam = (math.exp(float((v["lq1"] * v["lk1"]).sum())) - math.exp(float((v["lq2"] * v["lk2"]).sum()))
                         + float(self.differential["diff"]))
+        if self.mix_name:
+            self.mix = tensors[self.mix_name].contiguous()
+        if self.sink_name and self.sink_name != "zero":
+            self.sinks = tensors[self.sink_name].contiguous()
         if self.position:
             self.position.bind(tensors)
         if self.qk_transform:
@@ -196,10 +221,15 @@ class PagedAttention:
         q = self.qk_transform.prepare(qkv, ctx, cache, self)
         n = q.shape[0]
         attn = torch.empty((n, self.o_dim), dtype=self.dtype, device=q.device)
+        if self.mix is not None:
+            kernels.attention_mixed(attn, q, cache.k, cache.v, self.mix, ctx, cache.block_table, self.n_heads, self.n_kv,
+                                    self.head_dim, self.v_head_dim, self.window or 0, self.scale, sinks=self.sinks)
+            return attn
         if self.maps == 1:
             kernels.attention(attn, q, cache.k, cache.v, ctx, cache.block_table, self.n_heads, self.n_kv,
                               self.head_dim, self.window or 0, self.scale, score_slopes=self.score_slopes,
-                              v_head_dim=self.v_head_dim, exact_weights=self.exact_weights, segment=self.segment)
+                              v_head_dim=self.v_head_dim, exact_weights=self.exact_weights, segment=self.segment,
+                              sinks=self.sinks)
             return attn
         # two maps per head: 2H query heads over 2G key heads and G value heads, combined afterwards
         both = torch.empty((n, self.maps * self.o_dim), dtype=torch.float32, device=q.device)

@@ -5,6 +5,9 @@ output handed on as ``pending`` and added inside the next norm (the next layer's
 first norm, or the model's final norm), as the reference does
 (backend/model.cu:1068-1072, 1083-1089, 1105, 1117).
 
+``output_norm``: x += norm1(mixer(x)); x += norm2(ff(x)), the sublayers reading the stream itself, with an
+optional third sublayer that reads the step's token ids (``OutputNormBlock``).
+
 Interface of a block: ``forward(x, pending, ctx, cache) -> pending'``.  x is the
 float32 residual stream, updated in place; ``pending`` (float32 or model dtype, or
 None) is what is still to be added to x.
@@ -147,5 +150,101 @@ class SandwichNormBlock:
         return DeferredNorm(self.ff_post, self.feed_forward.forward(xn, ctx))
 
 
+class ReadyRows:
+    """Nothing is owed to the residual stream; the block before only hands on the stream's rows in the model
+    dtype, which it formed in its last kernel, for a block that would otherwise form them again."""
+
+    accepted_by = "accepts_ready_rows"
+
+    def __init__(self, rows):
+        self.rows = rows
+
+    def settle(self, x):
+        return None
+
+    def peek(self, x):
+        return x
+
+
+class OutputNormBlock:
+    """``output_norm``: a norm on each sublayer's OUTPUT only,
+
+        x += norm1(mixer(x));  x += norm2(ff(x));  x += side_norm(side(x, token))
+
+    The sublayers read the stream x itself (in the model dtype: for bfloat16 the rows rounded once, for
+    float32 the stream).  ``BlockSpec.mixer_norm`` / ``ff_norm`` are the norms behind the mixer and the
+    feed-forward (parts that offer ``add_normed``); ``feed_forward`` may be None.  ``params``: optional
+    ``side`` (a PartSpec of the side_input family: a third sublayer that also reads the step's token ids,
+    ``forward(h, ctx) -> float32 [n, hidden]``) with ``side_norm`` (its norm).  Every norm's kernel also
+    stores the updated rows in the model dtype, the next sublayer's input, also across blocks (``ReadyRows``)."""
+
+    accepts_ready_rows = True
+
+    def __init__(self, spec: BlockSpec, env: BuildEnv):
+        def norm(ps):
+            return part_factory("norm", ps.kind)(ps, env)
+        self.dtype = env.dtype
+        self.mixer = part_factory("mixer", spec.mixer.kind)(spec.mixer, env)
+        self.mixer_norm = norm(spec.mixer_norm)
+        self.feed_forward = self.ff_norm = self.side = self.side_norm = None
+        if spec.feed_forward is not None:
+            self.feed_forward = part_factory("feed_forward", spec.feed_forward.kind)(spec.feed_forward, env)
+            self.ff_norm = norm(spec.ff_norm)
+        side = spec.params.get("side")
+        if side is not None:
+            self.side = part_factory("side_input", side.kind)(side, env)
+            self.side_norm = norm(spec.params["side_norm"])
+
+    def parts(self):
+        return [p for p in (self.mixer, self.mixer_norm, self.feed_forward, self.ff_norm, self.side, self.side_norm)
+                if p is not None]
+
+    def tensor_specs(self):
+        return [s for p in self.parts() for s in p.tensor_specs()]
+
+    @property
+    def graph_safe(self):
+        return all(getattr(p, "graph_safe", True) for p in self.parts())
+
+    def bind(self, tensors):
+        for p in self.parts():
+            p.bind(tensors)
+
+    def _rows(self, x):
+        from .. import kernels
+        import torch
+        return x if self.dtype == torch.float32 else kernels.unary(x, "copy", self.dtype)
+
+    def _join(self, norm, x, y):
+        """x += norm(y); the updated rows in the model dtype (x itself when that is float32)."""
+        import torch
+        if self.dtype == torch.float32:
+            norm.add_normed(x, y)
+            return x
+        return norm.add_normed(x, y, then="rows")
+
+    def forward(self, x, pending, ctx, cache):
+        if isinstance(pending, ReadyRows):
+            h = pending.rows
+        else:
+            if hasattr(pending, "settle"):
+                pending = pending.settle(x)
+            if pending is not None:
+                x.add_(pending.float())
+            h = self._rows(x)
+        h = self._join(self.mixer_norm, x, self._f32(self.mixer.forward(h, ctx, cache)))
+        if self.feed_forward is not None:
+            h = self._join(self.ff_norm, x, self._f32(self.feed_forward.forward(h, ctx)))
+        if self.side is not None:
+            h = self._join(self.side_norm, x, self._f32(self.side.forward(h, ctx)))
+        return ReadyRows(h)
+
+    @staticmethod
+    def _f32(y):
+        import torch
+        return y if y.dtype == torch.float32 and y.is_contiguous() else y.float().contiguous()
+
+
 register_part("block", "pre_norm", PreNormBlock)
+register_part("block", "output_norm", OutputNormBlock)
 register_part("block", "sandwich_norm", SandwichNormBlock)

@@ -6,7 +6,8 @@ default 1) and ``tensor`` (the table's full name where it is not ``<prefix>.weig
 stream (reference backend/model.cu:89-95, no scaling for Llama).
 
 Head: params ``vocab``, ``width``, ``tied_to`` (name of the embedding tensor to
-share, or None), optional ``tensor`` (full name); tensor ``<prefix>.weight`` [vocab, width] unless tied;
+share, or None), optional ``tensor`` (full name), optional ``softcap`` (c > 0: the logits become
+c * tanh(logits / c), in float32, in place); tensor ``<prefix>.weight`` [vocab, width] unless tied;
 ``forward(xn) -> logits`` float32 [rows, vocab], accumulated in float32 (reference
 backend/model.cu:1187; tying resolved offline there, tools/convert_hf.py:81-82).
 """
@@ -44,6 +45,7 @@ class LinearHead:
         self.width = int(spec.params["width"])
         self.tied_to = spec.params.get("tied_to")
         self.name = spec.params.get("tensor") or spec.prefix + ".weight"
+        self.softcap = float(spec.params.get("softcap") or 0.0)
         self.weight = None
 
     def tensor_specs(self):
@@ -53,8 +55,13 @@ class LinearHead:
     def bind(self, tensors):
         self.weight = tensors[self.tied_to] if self.tied_to else tensors[self.name]
 
+    def _capped(self, logits):
+        if self.softcap > 0.0:
+            kernels.unary(logits, "softcap", torch.float32, arg=self.softcap, out=logits)
+        return logits
+
     def forward(self, xn):
-        return kernels.linear(xn, self.weight, out_dtype=torch.float32)
+        return self._capped(kernels.linear(xn, self.weight, out_dtype=torch.float32))
 
     def forward_normed(self, x, norm, rows):
         """Logits of rows ``rows`` of the float32 residual stream with ``norm`` applied
@@ -62,7 +69,8 @@ class LinearHead:
         n = rows.numel()
         if not (getattr(norm, "fusable_rmsnorm", False) and kernels.skinny_fits(n, self.width, self.weight.dtype)):
             return None
-        return kernels.skinny_gemm(self.weight, x_f32=x, gain=norm.gain, eps=norm.eps, rows=rows, epilogue="f32")
+        return self._capped(kernels.skinny_gemm(self.weight, x_f32=x, gain=norm.gain, eps=norm.eps, rows=rows,
+                                                epilogue="f32"))
 
 
 register_part("embedding", "token_embedding", TokenEmbedding)

@@ -35,8 +35,8 @@ the second form), ``rot_dim`` (dr, 0: the first form), ``rotary``, ``gate``, ``q
 ``kv_rank`` (R), ``scale``, ``eps`` (of both latent norms), ``window`` (None: every earlier
 key; W: the last W keys, the query's own included), ``cache_window`` (what the cache must
 keep: the widest window of all layers that read this cache; None: everything), ``sinks`` (True:
-a learned sink per head), ``own_latent`` (False: the layer reads the latents that another
-layer cached and has no W_dkv), ``tensors`` (dq, dq_norm, uq, dkv, dkv_norm, uk, uv, sink, o ->
+a learned sink per head), ``own_latent`` (False: the layer reads the rows that another
+layer cached, in the second form the latent and the rotated key part, and has no W_dkv), ``tensors`` (dq, dq_norm, uq, dkv, dkv_norm, uk, uv, sink, o ->
 full names).
 """
 from __future__ import annotations
@@ -85,11 +85,12 @@ class LatentAttention:
         n, d, H = self.names, self.hidden, self.H
         if self.dr:
             out = [TensorSpec(n["q"], (H * (self.dk + self.dr), d)),
-                   TensorSpec(n["dkv"], (self.R + self.dr, d)),
-                   TensorSpec(n["dkv_norm"], (self.R,), store="float32", init="gain"),
                    TensorSpec(n["uk"], (H * self.dk, self.R)),
                    TensorSpec(n["uv"], (H * self.dv, self.R)),
                    TensorSpec(n["o"], (d, H * self.dv))]
+            if self.own_latent:
+                out += [TensorSpec(n["dkv"], (self.R + self.dr, d)),
+                        TensorSpec(n["dkv_norm"], (self.R,), store="float32", init="gain")]
             if self.gate:
                 out.append(TensorSpec(n["g"], (H * self.dv, d)))
             if self.has_sinks:
@@ -116,9 +117,11 @@ class LatentAttention:
         self.sink = tensors[n["sink"]].contiguous() if self.has_sinks else None
         if self.dr:
             # queries, latent with the rotated key part, gate: one product
-            rows = [tensors[n["q"]], tensors[n["dkv"]]] + ([tensors[n["g"]]] if self.gate else [])
+            # (a layer that reads another layer's cached rows has no latent of its own: queries and gate alone)
+            rows = [tensors[n["q"]]] + ([tensors[n["dkv"]]] if self.own_latent else []) + \
+                ([tensors[n["g"]]] if self.gate else [])
             self.w_in = torch.cat(rows, dim=0).contiguous()
-            self.g_kv = tensors[n["dkv_norm"]]
+            self.g_kv = tensors[n["dkv_norm"]] if self.own_latent else None
             return
         self.w_dq = tensors[n["dq"]]
         # both down-projections are one product
@@ -158,7 +161,7 @@ class LatentAttention:
                               self.scale, v_head_dim=R, sinks=self.sink, exact_weights=True)
             o = kernels.linear_per_head(o_lat, self.w_uv)                                # [n, H * dv]
         if self.gate:
-            off = H * (self.dk + dr) + R + dr
+            off = H * (self.dk + dr) + (R + dr if self.own_latent else 0)
             kernels.sigmoid_gate(o, o, proj[:, off:off + H * self.dv])
         return kernels.linear(o, self.w_o, out_dtype=torch.float32, small_ok=True)
 

@@ -106,7 +106,7 @@ class GatedMLP:
 
 class PlainMLP:
     """Feed-forward without a gate: down(act(up x)).  params: ``hidden``, ``intermediate``,
-    ``activation`` ("relu2": the square of relu), optional ``tensors`` (up/down -> full
+    ``activation`` ("relu2": the square of relu; "gelu": with the error function; "gelu_tanh": its tanh form), optional ``tensors`` (up/down -> full
     names; default ``<prefix>.up`` and ``<prefix>.down``).  The up product's float32 result
     meets the activation unrounded; the result is float32 [n, hidden]."""
 
@@ -115,8 +115,8 @@ class PlainMLP:
         self.hidden = int(p["hidden"])
         self.inter = int(p["intermediate"])
         self.activation = p.get("activation", "relu2")
-        if self.activation not in ("relu2",):
-            raise ValueError(f"plain feed-forward: activation {self.activation!r} has no kernel (relu2 only)")
+        if self.activation not in ("relu2", "gelu", "gelu_tanh"):
+            raise ValueError(f"plain feed-forward: activation {self.activation!r} has no kernel (relu2, gelu, gelu_tanh)")
         names = dict(p.get("tensors") or {})
         self.up_name = names.get("up") or f"{spec.prefix}.up"
         self.down_name = names.get("down") or f"{spec.prefix}.down"

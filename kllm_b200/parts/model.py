@@ -14,8 +14,8 @@ from typing import Dict, List, Optional
 import torch
 
 # registering the built-in part kinds
-from . import (attention, block, embedding, latent_attention, mlp, moe, norm, qk_norm, rotary, streams,  # noqa: F401
-               wkv)
+from . import (attention, block, embedding, latent_attention, lightning, mlp, moe, norm, qk_norm, rotary,  # noqa: F401
+               side_input, streams, wkv)
 from .context import LayerCache, StepContext
 from .spec import BuildEnv, ModelSpec, PagedKVNeed, StateNeed, TensorSpec, part_factory
 

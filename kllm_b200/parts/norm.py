@@ -1,7 +1,9 @@
 """RMSNorm with the residual sum folded in, and layer norm with gain and bias (``LayerNorm``, at the end).
 
 params: ``width``, ``eps``, optional ``tensor`` (the gain's full name where it is not
-``<prefix>.weight``).  Tensor: ``<prefix>.weight`` [width], kept in float32
+``<prefix>.weight``), optional ``offset`` (the files hold the gain minus this number, e.g. a weight
+stored around zero that acts as 1 + w: the offset is added once, in float32, when the weights are bound;
+random weights then start at zero).  Tensor: ``<prefix>.weight`` [width], kept in float32
 (reference backend/model.cu:101-122, 144-165; the gain is used as stored, no 1 + w).
 Interface of a norm part:
 ``forward(x, res, rows=None) -> out``: x is the float32 residual stream [n, width];
@@ -10,7 +12,8 @@ result is in the model dtype.  With ``rows`` only those rows are normalised and 
 is left as it is.
 ``add_normed(x, y, then=None)``: x += rmsnorm(y) * gain for a float32 sublayer output y, the
 form of a norm that sits AFTER a sublayer; with ``then`` (another norm of this kind) it also
-returns that norm of the updated x, computed in the same kernel.
+returns that norm of the updated x, computed in the same kernel; with ``then="rows"`` it returns the
+updated rows themselves in the model dtype (for a sublayer that reads the stream without a norm in front).
 
 A part that can apply this norm inside its own kernel (see ``forward_residual`` of
 the attention and feed-forward parts) recognises it by ``fusable_rmsnorm`` and
@@ -31,14 +34,15 @@ class RMSNorm:
         self.width = int(spec.params["width"])
         self.eps = float(spec.params["eps"])
         self.name = spec.params.get("tensor") or spec.prefix + ".weight"
+        self.offset = float(spec.params.get("offset") or 0.0)
         self.dtype = env.dtype
         self.gain = None
 
     def tensor_specs(self):
-        return [TensorSpec(self.name, (self.width,), store="float32", init="gain")]
+        return [TensorSpec(self.name, (self.width,), store="float32", init="zeros" if self.offset else "gain")]
 
     def bind(self, tensors):
-        self.gain = tensors[self.name]
+        self.gain = tensors[self.name] + self.offset if self.offset else tensors[self.name]
 
     def forward(self, x, res=None, rows=None):
         n = x.shape[0] if rows is None else rows.numel()
@@ -52,6 +56,11 @@ class RMSNorm:
             kernels.rmsnorm_add(x, y, self.gain, self.eps)
             return None
         out = torch.empty(x.shape, dtype=self.dtype, device=x.device)
+        if isinstance(then, str):
+            if then != "rows":
+                raise ValueError(f"add_normed: then={then!r} (a norm, or 'rows')")
+            kernels.rmsnorm_add(x, y, self.gain, self.eps, out=out)
+            return out
         kernels.rmsnorm_add(x, y, self.gain, self.eps, out=out, gain2=then.gain, eps2=then.eps)
         return out
 

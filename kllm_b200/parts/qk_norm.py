@@ -6,7 +6,10 @@ a ``qk_transform`` of the attention mixer for layers without rotation.
     k <- k / sqrt(mean(k^2 over G * dk) + eps) * g_k
 
 params: ``q_dim`` (H * dk), ``k_dim`` (G * dk), ``eps``, ``q_gain`` / ``k_gain`` (full tensor
-names, plain gains, float32), ``temp_coef`` (0 or absent: no temperature), ``temp_every``.
+names, plain gains, float32), ``temp_coef`` (0 or absent: no temperature), ``temp_every``,
+``rotary_dim`` and ``theta`` (optional: AFTER the norm the first ``rotary_dim`` values of every query and
+key head are rotated, pair (i, i + rotary_dim / 2) by position * theta^(-2i / rotary_dim), the angle formed
+in double precision on the device, in the same kernel; ``scaling`` as in ``rotary.rotary_frequencies``).
 It offers ``prepare`` (see ``parts/attention.py``): it takes the projection's float32
 result, so sums, scales and the temperature are float32 in both dtypes, returns the queries
 in the model dtype and writes keys and values (of their own head size) into the layer's
@@ -32,6 +35,15 @@ class WholeProjectionNorm:
             raise ValueError(f"query temperature: period {self.every} must be positive")
         self.dtype = env.dtype
         self.q_gain = self.k_gain = None
+        self.rot, self.freq = int(p.get("rotary_dim") or 0), None
+        if self.rot:
+            from .rotary import rotary_frequencies
+            if self.rot % 2:
+                raise ValueError(f"rotary_dim {self.rot} must be even")
+            freq, amplitude = rotary_frequencies(self.rot, float(p["theta"]), p.get("scaling"))
+            if amplitude != 1.0:
+                raise ValueError("whole_rmsnorm: a rotation whose scaling changes the amplitude has no kernel here")
+            self.freq = freq.to(env.device)
 
     def tensor_specs(self):
         return [TensorSpec(self.q_name, (self.q_dim,), store="float32", init="gain"),
@@ -46,7 +58,7 @@ class WholeProjectionNorm:
         kernels.qknorm_append(q, qkv, self.q_gain, self.k_gain if writes else None, self.eps, self.coef, self.every,
                               ctx.positions, ctx.token_req, cache.block_table if writes else None,
                               cache.k if writes else None, cache.v if writes else None,
-                              attn.n_heads, attn.n_kv, attn.head_dim, attn.v_head_dim)
+                              attn.n_heads, attn.n_kv, attn.head_dim, attn.v_head_dim, rot=self.rot, freq=self.freq)
         return q
 
 

@@ -138,13 +138,13 @@ class StateNeed:
 
 _KINDS: Dict[str, Dict[str, Callable]] = {
     "mixer": {}, "feed_forward": {}, "norm": {}, "position": {}, "qk_transform": {}, "block": {},
-    "embedding": {}, "head": {},
+    "embedding": {}, "head": {}, "side_input": {},
 }
 
 
 def register_part(family: str, kind: str, factory: Callable) -> None:
     """``factory(spec: PartSpec, env: BuildEnv)`` returns the part.  ``family`` is one
-    of mixer, feed_forward, norm, position, qk_transform, block, embedding, head."""
+    of mixer, feed_forward, norm, position, qk_transform, block, embedding, head, side_input."""
     if family not in _KINDS:
         raise KeyError(f"unknown part family {family!r}; families: {sorted(_KINDS)}")
     _KINDS[family][kind] = factory
