@@ -72,19 +72,28 @@ def rotate(x, positions, dims, base):
 
 # ---- mixers -----------------------------------------------------------------------------
 
+def decayed_state_scan(q, k, v, decay, state=None):
+    """q, k [T, H, dk], v [T, H, dv], decay [H]: S_t = decay S_(t-1) + k_t v_t^T, o_t = S_t^T q_t, token by token.
+    Returns (o [T, H, dv], the last state [H, dk, dv])."""
+    T, H, dk = q.shape
+    dv = v.shape[2]
+    S = np.zeros((H, dk, dv)) if state is None else f64(state).copy()
+    o = np.zeros((T, H, dv))
+    for t in range(T):
+        for hd in range(H):
+            S[hd] = float(decay[hd]) * S[hd] + np.outer(k[t, hd], v[t, hd])
+            o[t, hd] = S[hd].T @ q[t, hd]
+    return o, S
+
+
 def lightning_mixer(h, w, p, m, eps):
-    """Linear attention with one fixed decay per head: S_t = decay S_(t-1) + k_t v_t^T, o_t = S_t^T q_t."""
+    """Linear attention with one fixed decay per head, one norm over all heads' outputs, a sigmoid gate."""
     T = h.shape[0]
     H, dk, dv = m["heads"], m["dim"], m["vdim"]
     q = silu(h @ f64(w[p + ".q"]).T).reshape(T, H, dk)
     k = silu(h @ f64(w[p + ".k"]).T).reshape(T, H, dk)
     v = silu(h @ f64(w[p + ".v"]).T).reshape(T, H, dv)
-    o = np.zeros((T, H, dv))
-    for hd in range(H):
-        S = np.zeros((dk, dv))
-        for t in range(T):
-            S = float(m["decay"][hd]) * S + np.outer(k[t, hd], v[t, hd])
-            o[t, hd] = S.T @ q[t, hd]
+    o, _ = decayed_state_scan(q, k, v, m["decay"])
     y = norm_plain(o.reshape(T, H * dv), w[p + ".norm"], eps) * sigmoid(h @ f64(w[p + ".g"]).T)
     return y @ f64(w[p + ".o"]).T
 
@@ -117,28 +126,48 @@ def latent_mixer(h, w, p, m, eps, positions, kv):
     return out.reshape(T, H * dv) @ f64(w[p + ".o"]).T
 
 
+def mixed_window_attention(q, k, v, talk, scale, size, positions=None, sink=True):
+    """q [T, H, dk] at ``positions`` (default 0 .. T-1) over keys k [S, G, dk] and values v [S, G, dv] at positions
+    0 .. S-1: the heads' scaled scores are mixed by ``talk`` [H, H], a query at p sees the keys j with
+    0 <= p - j < size (size None: every j <= p), and a sink of score 0 joins the softmax's denominator."""
+    q, k, v = f64(q), f64(k), f64(v)
+    T, H, _ = q.shape
+    G, dv = k.shape[1], v.shape[2]
+    per = H // G
+    positions = np.arange(T) if positions is None else np.asarray(positions)
+    raw = np.stack([q[:, hd] @ k[:, hd // per].T for hd in range(H)]) * scale             # [H, T, S]
+    mixed = np.einsum("hg,gij->hij", f64(talk), raw)
+    out = np.zeros((T, H, dv))
+    for i, p in enumerate(positions):
+        lo = 0 if size is None else max(0, p - size + 1)
+        for hd in range(H):
+            s = mixed[hd, i, lo:p + 1]
+            top = max(s.max(), 0.0) if sink else s.max()
+            e = np.exp(s - top)
+            out[i, hd] = (e / ((np.exp(-top) if sink else 0.0) + e.sum())) @ v[lo:p + 1, hd // per]
+    return out
+
+
+def normed_rotated_qk(qp, kp, q_gain, k_gain, eps, H, G, dk, positions, rot):
+    """RMS norm over each WHOLE projection (all heads at once, plain gains), then the rotation of every head."""
+    T = qp.shape[0]
+    q = norm_plain(qp, q_gain, eps).reshape(T, H, dk)
+    k = norm_plain(kp, k_gain, eps).reshape(T, G, dk)
+    if rot:
+        q, k = rotate(q, positions, rot["dims"], rot["base"]), rotate(k, positions, rot["dims"], rot["base"])
+    return q, k
+
+
 def window_attention_mixer(h, w, p, m, eps, positions):
     """Grouped attention with norms over the whole q and k projections, a partial rotation, scores
     mixed across the heads, a window and a sink of score 0."""
     T = h.shape[0]
     H, G, dk, dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
-    q = norm_plain(h @ f64(w[p + ".q"]).T, w[p + ".q.norm"], eps).reshape(T, H, dk)
-    k = norm_plain(h @ f64(w[p + ".k"]).T, w[p + ".k.norm"], eps).reshape(T, G, dk)
+    q, k = normed_rotated_qk(h @ f64(w[p + ".q"]).T, h @ f64(w[p + ".k"]).T, w[p + ".q.norm"], w[p + ".k.norm"], eps,
+                             H, G, dk, positions, m.get("rot"))
     v = (h @ f64(w[p + ".v"]).T).reshape(T, G, dv)
-    q = rotate(q, positions, m["rot"]["dims"], m["rot"]["base"])
-    k = rotate(k, positions, m["rot"]["dims"], m["rot"]["base"])
-    per = H // G
-    raw = np.stack([q[:, hd] @ k[:, hd // per].T for hd in range(H)]) * m["scale"]        # [H, T(query), T(key)]
-    mixed = np.einsum("hg,gij->hij", f64(w[p + ".talk"]), raw)
-    size = m["mask"]["size"]
-    out = np.zeros((T, H, dv))
-    for i in range(T):
-        lo = max(0, i - size + 1)
-        for hd in range(H):
-            s = mixed[hd, i, lo:i + 1]
-            top = max(s.max(), 0.0)
-            e = np.exp(s - top)
-            out[i, hd] = (e / (np.exp(-top) + e.sum())) @ v[lo:i + 1, hd // per]
+    size = m["mask"]["size"] if m.get("mask") else None
+    out = mixed_window_attention(q, k, v, w[p + ".talk"], m["scale"], size)
     return out.reshape(T, H * dv) @ f64(w[p + ".o"]).T
 
 
@@ -221,10 +250,11 @@ def tensor_shapes(cfg):
     return out
 
 
-def random_weights(cfg, seed, std=0.08):
-    """Weights that make every mechanism count: matrices N(0, std) scaled by 1 / sqrt(fan-in / 64), one-plus
-    weights around zero, plain weights around one, a head-mixing matrix near the identity with sizeable
-    off-diagonal terms."""
+def random_weights(cfg, seed, std=0.08, qk_boost=1.0):
+    """Weights that make every mechanism count, all of them bfloat16 numbers (both dtypes load the same model):
+    matrices N(0, std) scaled by 1 / sqrt(fan-in / 64), one-plus weights around zero, plain weights around one,
+    a head-mixing matrix near the identity with sizeable off-diagonal terms; ``qk_boost`` scales the attention
+    layers' query and key projections, which sharpens the attention."""
     rng = np.random.default_rng(seed)
     w = {}
     for name, shape in tensor_shapes(cfg).items():
@@ -237,8 +267,10 @@ def random_weights(cfg, seed, std=0.08):
         elif name in ("embed", "side.embed"):
             t = rng.standard_normal(shape)
         else:
-            t = rng.standard_normal(shape) * std * math.sqrt(64.0 / shape[1]) * 4.0
-        w[name] = t.astype(np.float32)
+            t = rng.standard_normal(shape) * std * math.sqrt(64.0 / shape[1]) * 1.5
+            if name.endswith((".mix.q", ".mix.k", ".mix.dkv")):
+                t = t * qk_boost
+        w[name] = round_bf16(t.astype(np.float32))
     return w
 
 
