@@ -46,6 +46,10 @@ work.  A record of its own; the default line does not change.
 latents in a window with sinks, several residual streams, experts assigned by a table).
 ``--design ronurax`` does the same for the Ronurax design (two-map attention in mask segments,
 attention through a latent with a rotated key part, layer norms, experts chosen within groups).
+``--design senulix`` measures the Senulix design (window attention with scores mixed across the heads,
+attention through a latent that a later layer reads again, linear attention with a fixed decay per head,
+output norms, a token side input) beside a dense Sozarax model of equal size, the closest existing design
+(a recurrent mixer, attention with norms over the whole projections, a plain feed-forward), and beside a Llama.
 """
 from __future__ import annotations
 
@@ -252,7 +256,7 @@ def main():
     ap.add_argument("--workload", default="", choices=["", "llama2-7b-mixed"],
                     help="llama2-7b-mixed: 32 requests, prompts uniform in [128, 3072], 128 new tokens each, through "
                          "the scheduler (a record of its own, not the bench line)")
-    ap.add_argument("--design", default="", choices=["", "sozarax", "nutizen", "ronurax"],
+    ap.add_argument("--design", default="", choices=["", "sozarax", "nutizen", "ronurax", "senulix"],
                     help="sozarax, nutizen, ronurax: prefill and decode of that design at two layer sizes beside a Llama of equal size, and "
                          "its kernels against their rooflines (a record of its own, not the bench line)")
     args = ap.parse_args()
@@ -666,6 +670,39 @@ def ronurax_config(width, layers, heads, kv_heads, head_dim, experts, top, exper
     return {"architecture": "Ronurax", "vocab": vocab, "width": width, "norm": {"eps": 1e-6},
             "layers": [{"type": "attention" if i % 2 == 0 else "latent_attention", "mixer": dict(att if i % 2 == 0 else lat),
                         "mlp": dict(moe)} for i in range(layers)]}
+
+
+def senulix_config(width, layers, heads, kv_heads, head_dim, ff, vocab, kv_rank, rot_dim, window, side_dim):
+    """A Senulix model of ``layers`` layers in the pattern window attention, latent attention, linear attention,
+    latent attention that reads the rows of the latent layer two before it; a dense feed-forward in every layer but
+    the linear-attention ones."""
+    att = {"heads": heads, "kv_heads": kv_heads, "dim": head_dim, "vdim": head_dim, "scale": head_dim ** -0.5,
+           "mask": {"size": window}, "rot": {"base": 50000.0, "dims": head_dim // 2}}
+    lat = {"heads": heads, "dim": head_dim, "rot_dim": rot_dim, "vdim": head_dim, "kv_rank": kv_rank,
+           "scale": (head_dim + rot_dim) ** -0.5, "rot": {"base": 50000.0, "dims": rot_dim}}
+    lig = {"heads": heads, "dim": head_dim, "vdim": head_dim,
+           "decay": [1.0 - 2.0 ** (-1.0 - 7.0 * h / max(1, heads - 1)) for h in range(heads)]}
+    dense = {"kind": "dense", "ff": ff}
+    out = []
+    for i in range(layers):
+        k = i % 4
+        if k == 0:
+            out.append({"type": "attention", "mixer": dict(att), "mlp": dict(dense)})
+        elif k == 1:
+            out.append({"type": "latent_attention", "mixer": dict(lat), "mlp": dict(dense)})
+        elif k == 2:
+            out.append({"type": "lightning", "mixer": dict(lig), "mlp": None})
+        else:
+            out.append({"type": "latent_attention", "mixer": dict(lat, kv_from=i - 2), "mlp": dict(dense)})
+    return {"architecture": "Senulix", "vocab": vocab, "width": width, "norm": {"eps": 1e-6},
+            "token_side": {"dim": side_dim}, "logit_softcap": 30.0, "layers": out}
+
+
+SENULIX_EXTRA = {
+    # name: key/value latent, rotated size, window, per-layer size of the token side table
+    "2048-wide": (128, 32, 1024, 128),
+    "4096-wide": (192, 64, 1024, 256),
+}
 
 
 RONURAX_EXTRA = {
@@ -1220,8 +1257,126 @@ def design_comparison(args):
             del wsets, dsets
         return rows
 
+    def senulix_rows(width, heads, kv, hd, window):
+        """The Senulix design's own kernels, each beside the kernel of the closest design that does the like work."""
+        rows = []
+        dev = "cuda"
+        A = heads * hd
+        esz = 2 if dtype == "bfloat16" else 4
+        hbm, tens = pk["hbm_gbs"] * 1e9, pk["bf16_tflops"] * 1e12
+        cores = 2 * 128 * kernels.sm_count() * 1.9e9        # float32 operations a second of the CUDA cores
+
+        def ctx_of(n_new, start):
+            import itertools
+            import types
+            S = len(n_new)
+            qs = torch.tensor([0] + list(itertools.accumulate(n_new)), dtype=torch.int32, device=dev)
+            return types.SimpleNamespace(
+                n_tokens=sum(n_new), n_requests=S, q_start=qs,
+                token_req=torch.repeat_interleave(torch.arange(S, dtype=torch.int32), torch.tensor(n_new)).to(dev),
+                start_pos=torch.tensor(start, dtype=torch.int32, device=dev),
+                positions=torch.cat([torch.arange(s, s + c, dtype=torch.int32) for s, c in zip(start, n_new)]).to(dev),
+                state_slots=torch.arange(S, dtype=torch.int32, device=dev), host_n_new=list(n_new),
+                host_start_pos=list(start), all_single=all(c == 1 for c in n_new),
+                max_ctx=max(s + c for s, c in zip(start, n_new)), split_bound=0, max_new=max(n_new))
+
+        def row(name, us, floor, bound, like=None):
+            rows.append({"kernel": name, "us": round(us, 1), "floor_us": round(floor, 2), "bound": bound,
+                         "times_floor": round(us / floor, 1) if floor > 0 else None, "like": like})
+
+        # ---- the two recurrences: a prompt (one request of T rows) and a decode step (B requests of one row) ----
+        for name, n_new, start in (("prefill", [T], [0]), ("decode", [1] * B, [ctx - 1] * B)):
+            c = ctx_of(n_new, start)
+            n = sum(n_new)
+            sets = rotate(lambda: [torch.randn(n, A, device=dev) * 0.1 for _ in range(3)] + [torch.randn(n, A, device=dev) - 3],
+                          16 * n * A)
+            states = rotate(lambda: torch.zeros(len(n_new), A * hd + width, device=dev), 4 * len(n_new) * A * hd)
+            decay = torch.linspace(0.9, 0.999, heads, device=dev)
+            w0, u = torch.zeros(A, device=dev), torch.zeros(A, device=dev)
+            it = [0]
+
+            def lightning():
+                i = it[0] = it[0] + 1
+                q, k, v, _ = sets[i % len(sets)]
+                kernels.lightning_scan(q, k, v, decay, states[i % len(states)], c, heads, hd, hd)
+
+            def wkv():
+                i = it[0] = it[0] + 1
+                r, k, v, z = sets[i % len(sets)]
+                kernels.wkv_scan(r, k, v, z, w0, u, states[i % len(states)], c, heads, hd)
+            # floor of both: the state read and written once, the rows read and written once, and four float32
+            # operations per state element and row on the CUDA cores
+            by = 8.0 * len(n_new) * A * hd + 16.0 * n * A
+            t_core = 4.0 * n * A * hd / cores * 1e6
+            floor = max(by / hbm * 1e6, t_core)
+            bound = "memory" if by / hbm * 1e6 >= t_core else "float32 cores"
+            row("lightning_scan " + name, timed(lightning, inner=4) * 1e3, floor, bound, like="wkv_scan " + name)
+            row("wkv_scan " + name, timed(wkv, inner=4) * 1e3, floor, bound)
+            del sets, states
+        # ---- attention in a window: scores mixed across the heads, beside Llama's kernels on the same cache and window ----
+        for name, n_new, start in (("prefill", [T], [0]), ("decode", [1] * B, [ctx - 1] * B)):
+            c = ctx_of(n_new, start)
+            n, S = sum(n_new), len(n_new)
+            per = -(-max(s + m for s, m in zip(start, n_new)) // page)
+            table = torch.arange(S * per, dtype=torch.int32, device=dev).view(S, per).contiguous()
+            caches = rotate(lambda: (torch.randn(S * per, kv, page, hd, device=dev).to(tdt),
+                                     torch.randn(S * per, kv, page, hd, device=dev).to(tdt)), 2 * S * per * kv * page * hd * esz)
+            q = (torch.randn(n, A, device=dev) * 0.2).to(tdt)
+            out = torch.empty_like(q)
+            mix = (torch.eye(heads, device=dev) + 0.1 * torch.randn(heads, heads, device=dev)).contiguous()
+            sinks = torch.zeros(heads, device=dev)
+            it = [0]
+            pairs = sum(min(window, p + 1) for s, m in zip(start, n_new) for p in range(s, s + m))   # visible (query, key) pairs
+            keys = sum(min(window + m - 1, s + m) for s, m in zip(start, n_new))                       # keys read at least once
+            by = keys * kv * hd * 2 * esz + 2 * n * A * esz
+            t_tensor = 4.0 * pairs * A / tens * 1e6 if dtype == "bfloat16" else 0.0
+            t_mix = 2.0 * pairs * heads * heads / cores * 1e6          # the mixing: heads^2 float32 multiply-adds a pair
+            floor = max(by / hbm * 1e6, t_tensor, t_mix)
+            bound = "memory" if floor == by / hbm * 1e6 else ("tensor" if floor == t_tensor else "float32 cores (mixing)")
+
+            def mixed():
+                i = it[0] = it[0] + 1
+                kc, vc = caches[i % len(caches)]
+                kernels.attention_mixed(out, q, kc, vc, mix, c, table, heads, kv, hd, hd, window, hd ** -0.5, sinks=sinks)
+
+            def plain(**kw):
+                def call():
+                    i = it[0] = it[0] + 1
+                    kc, vc = caches[i % len(caches)]
+                    kernels.attention(out, q, kc, vc, c, table, heads, kv, hd, window, hd ** -0.5, **kw)
+                return call
+            row("mixed attention " + name, timed(mixed, inner=2) * 1e3, floor, bound, like="sink attention " + name)
+            f2 = max(by / hbm * 1e6, t_tensor)
+            b2 = "memory" if f2 == by / hbm * 1e6 else "tensor"
+            row("sink attention " + name + " (unmixed, float32 weights)", timed(plain(sinks=sinks, exact_weights=True), inner=4) * 1e3,
+                f2, b2)
+            row("llama attention " + name + " (same window)", timed(plain(), inner=4) * 1e3, f2, b2)
+            del caches
+        return rows
+
     sizes = {}
     for name, (width, layers, heads, kv, hd, ff, E, top, eff, vocab) in DESIGN_SIZES.items():
+        if args.design == "senulix":
+            R, dr, window, side = SENULIX_EXTRA[name]
+            sen = senulix_config(width, layers, heads, kv, hd, ff, vocab, R, dr, window, side)
+            soz = sozarax_config(width, layers, heads, kv, hd, ff, E, top, eff, vocab)
+            for L in soz["layers"]:
+                L["mlp"] = {"kind": "dense", "ff": ff}
+            llama = dict(TINYLLAMA, num_hidden_layers=layers, hidden_size=width, num_attention_heads=heads,
+                         num_key_value_heads=kv, head_dim=hd, intermediate_size=ff, vocab_size=vocab,
+                         max_position_embeddings=max(ctx, T))
+            print(f"[bench] {name}: Senulix", file=sys.stderr, flush=True)
+            rec = {"layers": layers, "heads": heads, "kv_heads": kv, "head_dim": hd, "window": window, "kv_rank": R,
+                   "rot_dim": dr, "token_side": side, "ff": ff, "senulix": model_run(sen, vocab)}
+            print(f"[bench] {name}: Sozarax (dense) of equal size", file=sys.stderr, flush=True)
+            rec["sozarax_dense"] = model_run(soz, vocab)
+            print(f"[bench] {name}: Llama of equal size", file=sys.stderr, flush=True)
+            rec["llama"] = model_run(llama, vocab)
+            print(f"[bench] {name}: kernels", file=sys.stderr, flush=True)
+            rec["kernels"] = senulix_rows(width, heads, kv, hd, window)
+            sizes[name] = rec
+            torch.cuda.empty_cache()
+            continue
         if args.design == "ronurax":
             R, dr, segment, rtop, groups, keep = RONURAX_EXTRA[name]
             ron = ronurax_config(width, layers, heads, kv, hd, E, rtop, eff, vocab, R, dr, segment, groups, keep)
@@ -1269,7 +1424,8 @@ def design_comparison(args):
         sizes[name] = rec
         torch.cuda.empty_cache()
     sampler.stop()
-    print(json.dumps({"partial": f"{args.design.capitalize()} beside a Llama of equal size", "dtype": dtype, "prefill_tokens": T,
+    beside = "a dense Sozarax and a Llama" if args.design == "senulix" else "a Llama"
+    print(json.dumps({"partial": f"{args.design.capitalize()} beside {beside} of equal size", "dtype": dtype, "prefill_tokens": T,
                       "decode_batch": B, "decode_context": ctx, "data": "synthetic, random weights",
                       "peaks": pk, "clocks": sampler.summary(t_begin, time.time()), "sizes": sizes}))
     return 0

@@ -217,6 +217,279 @@ attention_mixed_kernel(T* __restrict__ out, const T* __restrict__ q, int64_t q_s
     }
 }
 
+
+// ---- the tensor-core form (bfloat16 portions) ---------------------------------------------------------
+// The same sums with the two products on the tensor cores (mma.sync m16n8k16, bfloat16 operands, float32
+// accumulators): a CTA takes a tile of 16 query rows and a block of HB output heads.  Per key tile it forms the raw
+// scores of ALL heads (every output head needs them all), mixes them for its own heads in float32 on the CUDA
+// cores, and keeps the output of its own heads in registers: 16 x HB x dv float32 values spread over the eight
+// warps as m16n8 accumulator tiles.  The weights stay float32 until they meet the values: they enter the second
+// product as two bfloat16 terms (the weight rounded, and what the rounding left), which keeps 16 bits of mantissa.
+// Shared memory: the Q tile of all heads, the K tile of all kv heads (its place is reused for the transposed V tile
+// of the block's own kv heads), the raw scores (their place is reused for the two-term weights), the mixed scores.
+constexpr int kTile = 16;       // query rows of a tile
+constexpr int kFrags = 16;      // m16n8 accumulator tiles a warp may own: HB * dv / 8 <= 8 * kFrags
+
+struct MmaShape {
+    int H, G, dk, dv, HB, TK;
+};
+
+__host__ __device__ inline int own_kv_heads(const MmaShape& s) {
+    const int per = s.H / s.G;
+    return (s.HB + per - 1) / per + 1;          // a block of HB heads touches at most this many kv heads
+}
+
+struct MmaLayout {
+    size_t q, k, raw, mixed, stats, mix, total;
+};
+
+__host__ __device__ inline MmaLayout mma_layout(const MmaShape& s) {
+    MmaLayout L;
+    size_t o = 0;
+    L.q = o;      o += (size_t)kTile * (s.H * s.dk + 8) * 2;
+    const size_t ktile = (size_t)s.TK * (s.G * s.dk + 8) * 2;
+    const size_t vtile = (size_t)own_kv_heads(s) * s.dv * (s.TK + 8) * 2;
+    L.k = o;      o += (ktile > vtile ? ktile : vtile);
+    const size_t raw = (size_t)s.H * kTile * (s.TK + 4) * 4;
+    const size_t pw = 2 * (size_t)s.HB * kTile * (s.TK + 8) * 2;
+    L.raw = o;    o += (raw > pw ? raw : pw);
+    L.mixed = o;  o += (size_t)s.HB * kTile * (s.TK + 4) * 4;
+    L.stats = o;  o += 3 * (size_t)s.HB * kTile * 4;
+    L.mix = o;    o += (size_t)s.HB * s.H * 4;
+    L.total = (o + 15) / 16 * 16;
+    return L;
+}
+
+__device__ __forceinline__ uint32_t ld32(const bf16* p) { return *reinterpret_cast<const uint32_t*>(p); }
+
+__device__ __forceinline__ void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                         uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+__global__ void __launch_bounds__(kThreads)
+attention_mixed_mma_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, int64_t q_stride,
+                           const bf16* __restrict__ kcache, const bf16* __restrict__ vcache,
+                           const float* __restrict__ mix, const float* __restrict__ sinks,
+                           const int* __restrict__ q_start, const int* __restrict__ start_pos,
+                           const int* __restrict__ block_table, int max_blocks, int n_requests, MmaShape sh, int page_size,
+                           int window, float scale) {
+    extern __shared__ __align__(16) unsigned char smraw[];
+    const int H = sh.H, G = sh.G, dk = sh.dk, dv = sh.dv, HB = sh.HB, TK = sh.TK;
+    const int per = H / G;
+    const MmaLayout L = mma_layout(sh);
+    const int QP = H * dk + 8, KP = G * dk + 8, VP = TK + 8, RP = TK + 4, PP = TK + 8;
+    bf16* Qs = reinterpret_cast<bf16*>(smraw + L.q);            // [16][QP]
+    bf16* Ks = reinterpret_cast<bf16*>(smraw + L.k);            // [TK][KP]
+    bf16* Vt = Ks;                                              // [own kv heads * dv][VP], after the scores
+    float* raw = reinterpret_cast<float*>(smraw + L.raw);       // [H][16][RP]
+    bf16* Ph = reinterpret_cast<bf16*>(smraw + L.raw);          // [HB][16][PP], after the mixing
+    bf16* Pl = Ph + (size_t)HB * kTile * PP;
+    float* mixed = reinterpret_cast<float*>(smraw + L.mixed);   // [HB][16][RP]
+    float* mx = reinterpret_cast<float*>(smraw + L.stats);      // [HB][16]
+    float* dn = mx + HB * kTile;
+    float* cr = dn + HB * kTile;
+    float* ms = reinterpret_cast<float*>(smraw + L.mix);        // [HB][H], times scale
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int fr = lane >> 2, fc = (lane & 3) * 2;              // a fragment's row and first column of this lane
+
+    const int h0 = blockIdx.y * HB;
+    const int nh = min(HB, H - h0);
+    const int c_first = h0 / per;                               // first kv head of the block's own heads
+    const int n_own = (h0 + nh - 1) / per - c_first + 1;
+    for (int i = tid; i < nh * H; i += kThreads) ms[i] = mix[(size_t)(h0 + i / H) * H + i % H] * scale;
+    griddep_wait();
+    griddep_launch();
+    int req = 0, tile = blockIdx.x;
+    for (; req < n_requests; req++) {
+        const int tiles = (q_start[req + 1] - q_start[req] + kTile - 1) / kTile;
+        if (tile < tiles) break;
+        tile -= tiles;
+    }
+    if (req >= n_requests) return;
+    const int row0 = q_start[req] + tile * kTile;
+    const int nq = min(kTile, q_start[req + 1] - row0);
+    const int p0 = start_pos[req] + tile * kTile;
+    const int hi = p0 + nq - 1;
+    const int lo = window > 0 ? max(0, p0 - window + 1) : 0;
+    const int* table = block_table + (int64_t)req * max_blocks;
+
+    // the Q tile of all heads, 16 bytes at a time; rows past the portion's end are zero
+    const int qv = H * dk / 8;
+    for (int i = tid; i < kTile * qv; i += kThreads) {
+        const int r = i / qv, c = i - r * qv;
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (r < nq) v = *reinterpret_cast<const uint4*>(q + (int64_t)(row0 + r) * q_stride + c * 8);
+        *reinterpret_cast<uint4*>(Qs + (size_t)r * QP + c * 8) = v;
+    }
+    for (int i = tid; i < HB * kTile; i += kThreads) {
+        const int h = h0 + i / kTile;
+        mx[i] = (sinks && h < H) ? sinks[h] : -INFINITY;
+        dn[i] = sinks ? 1.f : 0.f;
+    }
+    float acc[kFrags][4];
+#pragma unroll
+    for (int f = 0; f < kFrags; f++) acc[f][0] = acc[f][1] = acc[f][2] = acc[f][3] = 0.f;
+    const int ntv = dv / 8;                     // accumulator tiles of a head
+    const int n_tiles = nh * ntv;
+
+    for (int j0 = lo; j0 <= hi; j0 += TK) {
+        const int nk = min(TK, hi - j0 + 1);
+        __syncthreads();                        // the tile before has been used up
+        // (1) keys of all kv heads
+        const int kv8 = dk / 8;
+        for (int i = tid; i < TK * G * kv8; i += kThreads) {
+            const int jj = i / (G * kv8), rest = i - jj * (G * kv8), g = rest / kv8, c = rest - g * kv8;
+            uint4 v = make_uint4(0, 0, 0, 0);
+            if (jj < nk) {
+                const int pos = j0 + jj, lp = pos / page_size;
+                const int64_t page = table[lp];
+                if (page >= 0)
+                    v = *reinterpret_cast<const uint4*>(kcache + ((page * G + g) * page_size + (pos - lp * page_size)) * dk + c * 8);
+            }
+            *reinterpret_cast<uint4*>(Ks + (size_t)jj * KP + g * dk + c * 8) = v;
+        }
+        __syncthreads();
+        // (2) raw scores: a warp takes whole heads; A = the head's Q rows, B = its kv head's keys
+        for (int g = warp; g < H; g += kThreads / 32) {
+            float c[4][4];
+#pragma unroll
+            for (int nt = 0; nt < 4; nt++) c[nt][0] = c[nt][1] = c[nt][2] = c[nt][3] = 0.f;
+            const bf16* qa = Qs + (size_t)fr * QP + g * dk + fc;
+            const bf16* kb = Ks + (size_t)fr * KP + (g / per) * dk + fc;
+            for (int k0 = 0; k0 < dk; k0 += 16) {
+                const uint32_t a0 = ld32(qa + k0), a1 = ld32(qa + 8 * QP + k0), a2 = ld32(qa + k0 + 8), a3 = ld32(qa + 8 * QP + k0 + 8);
+#pragma unroll
+                for (int nt = 0; nt < 4; nt++)
+                    if (nt * 8 < TK) mma_bf16(c[nt], a0, a1, a2, a3, ld32(kb + (size_t)nt * 8 * KP + k0), ld32(kb + (size_t)nt * 8 * KP + k0 + 8));
+            }
+            float* rg = raw + (size_t)g * kTile * RP;
+#pragma unroll
+            for (int nt = 0; nt < 4; nt++)
+                if (nt * 8 < TK) {
+                    rg[fr * RP + nt * 8 + fc] = c[nt][0];
+                    rg[fr * RP + nt * 8 + fc + 1] = c[nt][1];
+                    rg[(fr + 8) * RP + nt * 8 + fc] = c[nt][2];
+                    rg[(fr + 8) * RP + nt * 8 + fc + 1] = c[nt][3];
+                }
+        }
+        __syncthreads();
+        // (3) the values of the block's own kv heads, transposed, over the keys' place; the mixing and the mask
+        for (int i = tid; i < TK * n_own * dv; i += kThreads) {
+            const int e = i % dv, rest = i / dv, c = rest % n_own, jj = rest / n_own;
+            bf16 v = __float2bfloat16_rn(0.f);
+            if (jj < nk) {
+                const int pos = j0 + jj, lp = pos / page_size;
+                const int64_t page = table[lp];
+                if (page >= 0) v = vcache[((page * G + c_first + c) * page_size + (pos - lp * page_size)) * dv + e];
+            }
+            Vt[(size_t)(c * dv + e) * VP + jj] = v;
+        }
+        const int hb4 = (nh + 3) / 4;
+        for (int it = tid; it < hb4 * kTile * TK; it += kThreads) {
+            const int jj = it % TK, i = (it / TK) % kTile, b0 = (it / (TK * kTile)) * 4;
+            const int pos = j0 + jj, pi = p0 + i;
+            const bool visible = jj < nk && i < nq && pos <= pi && (window <= 0 || pi - pos < window);
+            float a0 = -INFINITY, a1 = -INFINITY, a2 = -INFINITY, a3 = -INFINITY;
+            if (visible) {
+                const float* m0 = ms + (size_t)b0 * H;
+                const float* m1 = b0 + 1 < nh ? m0 + H : m0;
+                const float* m2 = b0 + 2 < nh ? m0 + 2 * H : m0;
+                const float* m3 = b0 + 3 < nh ? m0 + 3 * H : m0;
+                a0 = a1 = a2 = a3 = 0.f;
+                const float* rr = raw + (size_t)i * RP + jj;
+                for (int g = 0; g < H; g++) {
+                    const float r = rr[(size_t)g * kTile * RP];
+                    a0 = fmaf(m0[g], r, a0);
+                    a1 = fmaf(m1[g], r, a1);
+                    a2 = fmaf(m2[g], r, a2);
+                    a3 = fmaf(m3[g], r, a3);
+                }
+            }
+            mixed[((b0 + 0) * kTile + i) * RP + jj] = a0;
+            if (b0 + 1 < nh) mixed[((b0 + 1) * kTile + i) * RP + jj] = a1;
+            if (b0 + 2 < nh) mixed[((b0 + 2) * kTile + i) * RP + jj] = a2;
+            if (b0 + 3 < nh) mixed[((b0 + 3) * kTile + i) * RP + jj] = a3;
+        }
+        __syncthreads();
+        // (4) one warp per (head, row): maximum, two-term weights, denominator
+        for (int rw = warp; rw < nh * kTile; rw += kThreads / 32) {
+            const float s = lane < TK ? mixed[(size_t)rw * RP + lane] : -INFINITY;
+            const float m_old = mx[rw];
+            const float m_new = fmaxf(m_old, warp_max(s));
+            const float w = (s == -INFINITY) ? 0.f : expf(s - m_new);
+            const float c = (m_old == -INFINITY) ? 0.f : expf(m_old - m_new);
+            const float sum = warp_sum(w);
+            if (lane < TK) {
+                const bf16 wh = __float2bfloat16_rn(w);
+                Ph[(size_t)rw * PP + lane] = wh;
+                Pl[(size_t)rw * PP + lane] = __float2bfloat16_rn(w - __bfloat162float(wh));
+            }
+            if (lane == 0) {
+                mx[rw] = m_new;
+                dn[rw] = dn[rw] * c + sum;
+                cr[rw] = c;
+            }
+        }
+        __syncthreads();
+        // (5) the output tiles this warp owns: tile t = (head of the block, eight value channels)
+#pragma unroll
+        for (int f = 0; f < kFrags; f++) {
+            const int t = warp + f * (kThreads / 32);
+            if (t < n_tiles) {
+                const int hb = t / ntv, nt = t - hb * ntv;
+                const float c_lo = cr[hb * kTile + fr], c_hi = cr[hb * kTile + fr + 8];
+                acc[f][0] *= c_lo; acc[f][1] *= c_lo; acc[f][2] *= c_hi; acc[f][3] *= c_hi;
+                const bf16* pa = Ph + (size_t)(hb * kTile + fr) * PP + fc;
+                const bf16* pb = Pl + (size_t)(hb * kTile + fr) * PP + fc;
+                const bf16* vb = Vt + (size_t)(((h0 + hb) / per - c_first) * dv + nt * 8 + fr) * VP + fc;
+                for (int k0 = 0; k0 < TK; k0 += 16) {
+                    const uint32_t b0 = ld32(vb + k0), b1 = ld32(vb + k0 + 8);
+                    mma_bf16(acc[f], ld32(pa + k0), ld32(pa + 8 * PP + k0), ld32(pa + k0 + 8), ld32(pa + 8 * PP + k0 + 8), b0, b1);
+                    mma_bf16(acc[f], ld32(pb + k0), ld32(pb + 8 * PP + k0), ld32(pb + k0 + 8), ld32(pb + 8 * PP + k0 + 8), b0, b1);
+                }
+            }
+        }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int f = 0; f < kFrags; f++) {
+        const int t = warp + f * (kThreads / 32);
+        if (t < n_tiles) {
+            const int hb = t / ntv, nt = t - hb * ntv;
+            const int col = (h0 + hb) * dv + nt * 8 + fc;
+            const float d_lo = dn[hb * kTile + fr], d_hi = dn[hb * kTile + fr + 8];
+            if (fr < nq) {
+                const float inv = d_lo > 0.f ? 1.f / d_lo : 0.f;
+                *reinterpret_cast<__nv_bfloat162*>(out + (int64_t)(row0 + fr) * H * dv + col) =
+                    __floats2bfloat162_rn(acc[f][0] * inv, acc[f][1] * inv);
+            }
+            if (fr + 8 < nq) {
+                const float inv = d_hi > 0.f ? 1.f / d_hi : 0.f;
+                *reinterpret_cast<__nv_bfloat162*>(out + (int64_t)(row0 + fr + 8) * H * dv + col) =
+                    __floats2bfloat162_rn(acc[f][2] * inv, acc[f][3] * inv);
+            }
+        }
+    }
+}
+
+// The block of heads and the key tile of the tensor-core form for these sizes; HB 0: the form does not take them.
+inline MmaShape mma_shape(int H, int G, int dk, int dv) {
+    MmaShape s = {H, G, dk, dv, 0, 0};
+    if (dk % 16 || dv % 16 || dv > 8 * kFrags * 8) return s;
+    int hb = 8 * kFrags * 8 / dv;
+    if (hb > H) hb = H;
+    for (int tk = 32; tk >= 16; tk /= 2) {
+        s.HB = hb;
+        s.TK = tk;
+        if (mma_layout(s).total <= 220 * 1024) return s;
+    }
+    s.HB = 0;
+    return s;
+}
+
 }  // namespace
 
 // out [n][H * dv] contiguous and q [n][H * dk] (row stride q_stride) in the element type `dtype`, which is also
@@ -271,4 +544,37 @@ extern "C" int kllm_attention_mixed_tile_rows(int n_heads, int n_kv, int dk, int
     while (sh.TQ > 1 && smem_floats(sh) * sizeof(float) > 200 * 1024) sh.TQ /= 2;
     while (sh.TK > 4 && smem_floats(sh) * sizeof(float) > 200 * 1024) sh.TK /= 2;
     return smem_floats(sh) * sizeof(float) > 200 * 1024 ? 0 : sh.TQ;
+}
+
+// Whether the tensor-core form takes these sizes (bfloat16; head sizes in steps of 16; shared memory).
+extern "C" int kllm_attention_mixed_mma_fits(int n_heads, int n_kv, int dk, int dv) {
+    if (n_heads <= 0 || n_kv <= 0 || n_heads % n_kv || dk <= 0 || dv <= 0) return 0;
+    return mma_shape(n_heads, n_kv, dk, dv).HB > 0 ? 1 : 0;
+}
+
+// The tensor-core form for bfloat16 portions: operands as in kllm_attention_mixed; n_tiles: an upper bound of the tiles of
+// 16 rows (sum over requests of ceil(rows / 16)); q rows and the caches' rows 16-byte aligned.
+extern "C" int kllm_attention_mixed_mma(void* out, const void* q, int64_t q_stride, const void* kcache, const void* vcache,
+                                        const float* mix, const float* sinks, const int* q_start, const int* start_pos,
+                                        const int* block_table, int max_blocks, int n_requests, int n_tiles, int n_heads,
+                                        int n_kv, int dk, int dv, int page_size, int window, float scale, void* stream) {
+    if (n_requests <= 0 || n_tiles <= 0) return 0;
+    if (n_heads <= 0 || n_kv <= 0 || n_heads % n_kv || page_size <= 0)
+        KLLM_FAIL("mixed attention: %d heads on %d kv heads", n_heads, n_kv);
+    const MmaShape sh = mma_shape(n_heads, n_kv, dk, dv);
+    if (sh.HB <= 0) KLLM_FAIL("mixed attention (tensor cores): head sizes %d, %d of %d heads are not taken", dk, dv, n_heads);
+    if (((uintptr_t)q & 15) || (q_stride % 8) || ((uintptr_t)kcache & 15) || ((uintptr_t)out & 3))
+        KLLM_FAIL("mixed attention (tensor cores): rows must be 16-byte aligned");
+    const size_t smem = mma_layout(sh).total;
+    static bool raised = false;
+    if (smem > 48 * 1024 && !raised) {
+        cudaError_t e = cudaFuncSetAttribute(attention_mixed_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
+        if (e != cudaSuccess) KLLM_FAIL("mixed attention (tensor cores): %s", cudaGetErrorString(e));
+        raised = true;
+    }
+    const int groups = (n_heads + sh.HB - 1) / sh.HB;
+    kllm_launch((attention_mixed_mma_kernel), dim3(n_tiles, groups), dim3(kThreads), smem, (cudaStream_t)stream, (bf16*)out,
+                (const bf16*)q, q_stride, (const bf16*)kcache, (const bf16*)vcache, mix, sinks, q_start, start_pos, block_table,
+                max_blocks, n_requests, sh, page_size, window, scale);
+    KLLM_LAUNCH_STATUS();
 }

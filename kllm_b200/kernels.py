@@ -1454,6 +1454,7 @@ def lightning_gate_norm(o: torch.Tensor, g: torch.Tensor, gain: torch.Tensor, ep
 # ---- attention with scores mixed across the heads (csrc/attention_mixed.cu) ---------------
 
 _mixed_tile_rows = {}
+MIXED_MMA = os.environ.get("KLLM_B200_MIXED_MMA", "1") != "0"     # bfloat16 portions on the tensor-core form
 
 
 def attention_mixed(out: torch.Tensor, q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, mix: torch.Tensor,
@@ -1462,8 +1463,10 @@ def attention_mixed(out: torch.Tensor, q: torch.Tensor, kcache: torch.Tensor, vc
     """Causal grouped attention of the step's tokens over the paged cache whose scaled scores are mixed across the
     heads before mask and softmax: s_h = sum_g mix[h, g] * scale * q_g . k_kv(g); ``mix`` float32 [H, H]; ``window``
     W > 0: a query sees the last W keys, its own included; ``sinks`` (float32 [H]): exp(sinks[h]) joins the
-    denominator of head h.  Scores, mixing, weights and sums are float32 in both dtypes.  Single tokens run as tiles
-    of one row, portions as tiles of up to eight rows of one request."""
+    denominator of head h.  Scores, mixing, weights and sums are float32 in both dtypes.  Two forms: on the CUDA
+    cores, single tokens as tiles of one row and portions as tiles of up to eight rows of one request (float32, and
+    every decoding step); on the tensor cores (mma.sync, bfloat16 steps that hold a portion, head sizes in steps of
+    16), tiles of 16 rows by a block of heads, the weights entering the second product as two bfloat16 terms."""
     _cuda(out, q, kcache, vcache, mix, block_table, sinks)
     _i32(block_table, "block_table"); _i32(ctx.q_start, "q_start"); _i32(ctx.start_pos, "start_pos")
     _slopes_arg(sinks, n_heads, "sinks")
@@ -1479,6 +1482,15 @@ def attention_mixed(out: torch.Tensor, q: torch.Tensor, kcache: torch.Tensor, vc
         raise KernelError("attention_mixed: the mixing matrix must be contiguous float32 [heads, heads]")
     lib = load_library("attention_mixed")
     key = (n_heads, n_kv, head_dim, v_head_dim)
+    if (MIXED_MMA and q.dtype == torch.bfloat16 and not ctx.all_single and q.data_ptr() % 16 == 0 and q.stride(0) % 8 == 0
+            and lib.kllm_attention_mixed_mma_fits(*key)):
+        tiles = ctx.n_tokens // 16 + ctx.n_requests
+        rc = lib.kllm_attention_mixed_mma(_p(out), _p(q), ctypes.c_int64(q.stride(0)), _p(kcache), _p(vcache), _p(mix),
+                                          _p(sinks), _p(ctx.q_start), _p(ctx.start_pos), _p(block_table),
+                                          block_table.shape[1], ctx.n_requests, int(tiles), n_heads, n_kv, head_dim,
+                                          v_head_dim, page_size, int(window or 0), ctypes.c_float(scale), _stream())
+        _check(lib, "attention_mixed", rc)
+        return
     if key not in _mixed_tile_rows:
         _mixed_tile_rows[key] = int(lib.kllm_attention_mixed_tile_rows(*key))
     rows = _mixed_tile_rows[key]

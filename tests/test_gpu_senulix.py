@@ -363,7 +363,7 @@ def test_whole_projection_norm_rotation_and_cache_write(dtype, H, G, dk, dv, rot
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("H,G,dk,dv,window", [(4, 2, 16, 24, 40), (6, 3, 8, 4, 33), (3, 1, 10, 6, 16), (8, 2, 64, 64, 64),
-                                              (40, 2, 16, 16, 100), (2, 2, 32, 64, 0), (5, 5, 12, 8, 1)])
+                                              (40, 2, 16, 16, 100), (2, 2, 32, 64, 0), (5, 5, 12, 8, 1), (32, 8, 128, 128, 48)])
 def test_mixed_attention_window_edges_far_keys_and_page_borders(dtype, H, G, dk, dv, window):
     """Scores mixed across the heads with a matrix far from the identity.  For every probed query one key is made
     to stand out (a large score in one head, which the mixing spreads to the others): the key just inside the
@@ -431,6 +431,38 @@ def test_mixed_attention_window_edges_far_keys_and_page_borders(dtype, H, G, dk,
     kernels.attention_mixed(out, qt, kct, vct, _t(talk), ctx, _t(table, "int32"), H, G, dk, dv, window, scale)
     plain = P.mixed_window_attention(q, k, v, talk, scale, W, sink=False).reshape(T, H * dv)
     assert np.abs(out.float().cpu().numpy() - plain).max() <= tol * np.abs(plain).max(), "no sink"
+
+
+@pytest.mark.parametrize("H,G,dk,dv", [(8, 2, 64, 64), (32, 8, 128, 128), (6, 3, 16, 48), (20, 1, 16, 32)])
+def test_mixed_attention_forms_agree(H, G, dk, dv):
+    """bfloat16 portions: the tensor-core form against the CUDA-core form on the same operands (both keep scores,
+    mixing and weights in float32, so they differ by the order of sums and the weights' second bfloat16 term)."""
+    import torch
+    from kllm_b200 import kernels
+    from kllm_b200.csrc.build import load_library
+    assert load_library("attention_mixed").kllm_attention_mixed_mma_fits(H, G, dk, dv)
+    g = torch.Generator(device="cuda").manual_seed(H)
+    T, page, window = 200, 16, 70
+    pages = -(-T // page)
+    q = (torch.randn(T, H * dk, device="cuda", generator=g) * 0.3).bfloat16()
+    kc = (torch.randn(pages, G, page, dk, device="cuda", generator=g) * 0.3).bfloat16()
+    vc = torch.randn(pages, G, page, dv, device="cuda", generator=g).bfloat16()
+    mix = (torch.eye(H, device="cuda") + 0.3 * torch.randn(H, H, device="cuda", generator=g)).contiguous()
+    table = torch.arange(pages, dtype=torch.int32, device="cuda").view(1, pages).repeat(3, 1).contiguous()
+    ctx = _ctx([1, 150, 37], [199, 13, 0])
+    rows = torch.tensor([199] + list(range(13, 163)) + list(range(37)), device="cuda")
+    outs = []
+    try:
+        for form in (True, False):
+            kernels.MIXED_MMA = form
+            out = torch.empty((len(rows), H * dv), dtype=torch.bfloat16, device="cuda")
+            kernels.attention_mixed(out, q[rows], kc, vc, mix, ctx, table, H, G, dk, dv, window, dk ** -0.5,
+                                    sinks=torch.zeros(H, device="cuda"))
+            outs.append(out.float())
+    finally:
+        kernels.MIXED_MMA = True
+    assert float((outs[0] - outs[1]).abs().max()) <= 2e-2 * float(outs[1].abs().max())
+    assert float((outs[0] - outs[1]).abs().mean()) <= 2e-3 * float(outs[1].abs().max())
 
 
 def test_shared_latent_reads_the_other_layers_rows(tmp_path):
