@@ -40,6 +40,7 @@ struct Shape {
 __host__ __device__ inline size_t smem_floats(const Shape& s) {
     const size_t kv = (size_t)s.TK * (size_t)((s.G * s.dk > s.G * s.dv ? s.G * s.dk : s.G * s.dv) + 1);
     return (size_t)s.TQ * s.H * s.dk            // q
+           + 2 * (size_t)s.TK                   // where each key of the tile lies (a 64-bit offset)
            + (size_t)s.H * s.H                  // M
            + kv                                 // K tile, then V tile
            + 2 * (size_t)s.H * s.TQ * s.TK      // raw, mixed / weights
@@ -47,9 +48,62 @@ __host__ __device__ inline size_t smem_floats(const Shape& s) {
            + (size_t)s.TQ * s.H * s.dv;         // output
 }
 
+// Where the keys j0 .. j0 + TK - 1 of a request lie: (page * G * page_size + slot), the row of kv head 0 in units of
+// rows, or -1 past the last key or without a page.  One look-up per key and tile, before the loads that use it.
+__device__ __forceinline__ void locate_keys(long long* where, const int* table, int j0, int nk, int TK, int G,
+                                            int page_size) {
+    for (int jj = threadIdx.x; jj < TK; jj += kThreads) {
+        long long w = -1;
+        if (jj < nk) {
+            const int pos = j0 + jj, lp = pos / page_size;
+            const long long page = table[lp];
+            if (page >= 0) w = page * G * page_size + (pos - lp * page_size);
+        }
+        where[jj] = w;
+    }
+}
+
+// A tile of keys or values into shared memory as float32: dst[jj][g * size + d] at row pitch `pitch`, from a store
+// [pages][G][page_size][size]; rows that `where` marks absent are zero.  bfloat16 rows in whole 16-byte pieces are
+// read as such.
+template <typename T>
+__device__ __forceinline__ void load_rows(float* dst, int pitch, const T* __restrict__ cache, const long long* where, int nk,
+                                          int G, int size, int page_size) {
+    const int w = G * size;
+    if (sizeof(T) == 2 && size % 8 == 0) {
+        const int w8 = w / 8, s8 = size / 8;
+        for (int i = threadIdx.x; i < nk * w8; i += kThreads) {
+            const int jj = i / w8, c = i - jj * w8, g = c / s8, d = (c - g * s8) * 8;
+            float* o = dst + jj * pitch + g * size + d;
+            const long long at = where[jj];
+            if (at < 0) {
+#pragma unroll
+                for (int u = 0; u < 8; u++) o[u] = 0.f;
+            } else {
+                const uint4 v = *reinterpret_cast<const uint4*>(cache + (at + (long long)g * page_size) * size + d);
+                const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+                for (int u = 0; u < 4; u++) {
+                    const float2 f = __bfloat1622float2(h[u]);
+                    o[2 * u] = f.x;
+                    o[2 * u + 1] = f.y;
+                }
+            }
+        }
+        return;
+    }
+#pragma unroll 4
+    for (int i = threadIdx.x; i < nk * w; i += kThreads) {
+        const int jj = i / w, c = i - jj * w, g = c / size, d = c - g * size;
+        const long long at = where[jj];
+        dst[jj * pitch + c] = at < 0 ? 0.f : to_f32(cache[(at + (long long)g * page_size) * size + d]);
+    }
+}
+
 template <typename T>
 __global__ void __launch_bounds__(kThreads)
-attention_mixed_kernel(T* __restrict__ out, const T* __restrict__ q, int64_t q_stride, const T* __restrict__ kcache,
+attention_mixed_kernel(T* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml,
+                       const T* __restrict__ q, int64_t q_stride, const T* __restrict__ kcache,
                        const T* __restrict__ vcache, const float* __restrict__ mix, const float* __restrict__ sinks,
                        const int* __restrict__ q_start, const int* __restrict__ start_pos,
                        const int* __restrict__ block_table, int max_blocks, int n_requests, Shape sh, int page_size,
@@ -59,7 +113,8 @@ attention_mixed_kernel(T* __restrict__ out, const T* __restrict__ q, int64_t q_s
     const int per = H / G;
     const int kw = G * dk, vw = G * dv;
     const int kp = (kw > vw ? kw : vw) + 1;                 // pitch of the K / V tile: odd, so that keys fall into different banks
-    float* qs = sm;                                         // [TQ][H * dk], scaled
+    long long* where = reinterpret_cast<long long*>(sm);    // [TK]: where each key of the tile lies
+    float* qs = sm + 2 * TK;                                // [TQ][H * dk], scaled
     float* ms = qs + (size_t)TQ * H * dk;                   // [H][H]
     float* kt = ms + H * H;                                 // [TK][kp]
     float* raw = kt + (size_t)TK * kp;                      // [H][TQ][TK]
@@ -84,9 +139,17 @@ attention_mixed_kernel(T* __restrict__ out, const T* __restrict__ q, int64_t q_s
     const int row0 = q_start[req] + tile * TQ;
     const int nq = min(TQ, q_start[req + 1] - row0);
     const int p0 = start_pos[req] + tile * TQ;              // position of the tile's first row
-    const int hi = p0 + nq - 1;                             // last key any row sees
-    const int lo = window > 0 ? max(0, p0 - window + 1) : 0;
+    int hi = p0 + nq - 1;                                   // last key any row sees
+    int lo = window > 0 ? max(0, p0 - window + 1) : 0;
     const int* table = block_table + (int64_t)req * max_blocks;
+    // with gridDim.y > 1 (single tokens) the keys are cut into that many ranges of whole tiles, one CTA each; the
+    // sink belongs to the first range, and a merging kernel joins the ranges' maxima, denominators and sums
+    const int splits = gridDim.y, split = blockIdx.y;
+    if (splits > 1) {
+        const int chunk = (((hi - lo + 1) + splits - 1) / splits + TK - 1) / TK * TK;
+        lo += split * chunk;
+        hi = min(hi, lo + chunk - 1);
+    }
 
     for (int i = tid; i < nq * H * dk; i += kThreads) {
         const int r = i / (H * dk), c = i - r * (H * dk);
@@ -94,22 +157,18 @@ attention_mixed_kernel(T* __restrict__ out, const T* __restrict__ q, int64_t q_s
     }
     for (int i = tid; i < H * TQ; i += kThreads) {
         const int h = i / TQ;
-        mx[i] = sinks ? sinks[h] : -INFINITY;
-        dn[i] = sinks ? 1.f : 0.f;
+        mx[i] = (sinks && split == 0) ? sinks[h] : -INFINITY;
+        dn[i] = (sinks && split == 0) ? 1.f : 0.f;
     }
     for (int i = tid; i < TQ * H * dv; i += kThreads) acc[i] = 0.f;
 
     for (int j0 = lo; j0 <= hi; j0 += TK) {
         const int nk = min(TK, hi - j0 + 1);
         __syncthreads();                                    // the tile before has been used up (and qs, mx, acc are set)
+        locate_keys(where, table, j0, nk, TK, G, page_size);
+        __syncthreads();
         // (1) keys
-        for (int i = tid; i < nk * kw; i += kThreads) {
-            const int jj = i / kw, c = i - jj * kw, g = c / dk, d = c - g * dk;
-            const int pos = j0 + jj, lp = pos / page_size;
-            const int64_t page = table[lp];
-            kt[jj * kp + c] = page < 0 ? 0.f
-                                       : to_f32(kcache[((page * G + g) * page_size + (pos - lp * page_size)) * dk + d]);
-        }
+        load_rows<T>(kt, kp, kcache, where, nk, G, dk, page_size);
         __syncthreads();
         // (2) raw scores of the query heads of one kv head, for one row and one key
         for (int it = tid; it < G * nq * TK; it += kThreads) {
@@ -135,13 +194,7 @@ attention_mixed_kernel(T* __restrict__ out, const T* __restrict__ q, int64_t q_s
         }
         __syncthreads();
         // (3) values over the keys' place; mixing and mask
-        for (int i = tid; i < nk * vw; i += kThreads) {
-            const int jj = i / vw, c = i - jj * vw, g = c / dv, d = c - g * dv;
-            const int pos = j0 + jj, lp = pos / page_size;
-            const int64_t page = table[lp];
-            kt[jj * kp + c] = page < 0 ? 0.f
-                                       : to_f32(vcache[((page * G + g) * page_size + (pos - lp * page_size)) * dv + d]);
-        }
+        load_rows<T>(kt, kp, vcache, where, nk, G, dv, page_size);
         const int hb = (H + 3) / 4;
         for (int it = tid; it < hb * nq * TK; it += kThreads) {
             const int jj = it % TK, i = (it / TK) % nq, h0 = (it / (TK * nq)) * 4;
@@ -210,10 +263,45 @@ attention_mixed_kernel(T* __restrict__ out, const T* __restrict__ q, int64_t q_s
         }
     }
     __syncthreads();
+    if (splits > 1) {
+        // TQ is 1: this range's unnormalised sums, maxima and denominators of the token's heads
+        float* po = part_o + ((size_t)row0 * splits + split) * H * dv;
+        for (int i = tid; i < H * dv; i += kThreads) po[i] = acc[i];
+        float* pm = part_ml + ((size_t)row0 * splits + split) * H * 2;
+        for (int h = tid; h < H; h += kThreads) {
+            pm[2 * h] = mx[h];
+            pm[2 * h + 1] = dn[h];
+        }
+        return;
+    }
     for (int i = tid; i < nq * H * dv; i += kThreads) {
         const int r = i / (H * dv), c = i - r * (H * dv), h = c / dv;
         const float d = dn[h * TQ + r];
         out[(int64_t)(row0 + r) * H * dv + c] = from_f32<T>(d > 0.f ? acc[i] / d : 0.f);
+    }
+}
+
+// Joins the key ranges of single tokens: out[t][h][:] = sum_s e^(m_s - M) acc_s / sum_s e^(m_s - M) l_s, in range order.
+template <typename T>
+__global__ void __launch_bounds__(kThreads)
+attention_mixed_merge_kernel(T* __restrict__ out, const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                             int splits, int H, int dv) {
+    griddep_wait();
+    griddep_launch();
+    const int t = blockIdx.x;
+    for (int i = threadIdx.x; i < H * dv; i += kThreads) {
+        const int h = i / dv;
+        const float* pm = part_ml + (size_t)t * splits * H * 2 + 2 * h;
+        float M = -INFINITY;
+        for (int s = 0; s < splits; s++) M = fmaxf(M, pm[(size_t)s * H * 2]);
+        float num = 0.f, den = 0.f;
+        for (int s = 0; s < splits; s++) {
+            const float m = pm[(size_t)s * H * 2];
+            const float w = (m == -INFINITY) ? 0.f : expf(m - M);
+            num = fmaf(w, part_o[((size_t)t * splits + s) * H * dv + i], num);
+            den = fmaf(w, pm[(size_t)s * H * 2 + 1], den);
+        }
+        out[(size_t)t * H * dv + i] = from_f32<T>(den > 0.f ? num / den : 0.f);
     }
 }
 
@@ -240,7 +328,7 @@ __host__ __device__ inline int own_kv_heads(const MmaShape& s) {
 }
 
 struct MmaLayout {
-    size_t q, k, raw, mixed, stats, mix, total;
+    size_t q, k, raw, mixed, stats, mix, where, total;
 };
 
 __host__ __device__ inline MmaLayout mma_layout(const MmaShape& s) {
@@ -255,7 +343,8 @@ __host__ __device__ inline MmaLayout mma_layout(const MmaShape& s) {
     L.raw = o;    o += (raw > pw ? raw : pw);
     L.mixed = o;  o += (size_t)s.HB * kTile * (s.TK + 4) * 4;
     L.stats = o;  o += 3 * (size_t)s.HB * kTile * 4;
-    L.mix = o;    o += (size_t)s.HB * s.H * 4;
+    L.mix = o;    o += ((size_t)s.HB * s.H * 4 + 15) / 16 * 16;
+    L.where = o;  o += (size_t)s.TK * 8;
     L.total = (o + 15) / 16 * 16;
     return L;
 }
@@ -292,6 +381,7 @@ attention_mixed_mma_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, i
     float* dn = mx + HB * kTile;
     float* cr = dn + HB * kTile;
     float* ms = reinterpret_cast<float*>(smraw + L.mix);        // [HB][H], times scale
+    long long* where = reinterpret_cast<long long*>(smraw + L.where);   // [TK]
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int fr = lane >> 2, fc = (lane & 3) * 2;              // a fragment's row and first column of this lane
 
@@ -338,17 +428,16 @@ attention_mixed_mma_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, i
     for (int j0 = lo; j0 <= hi; j0 += TK) {
         const int nk = min(TK, hi - j0 + 1);
         __syncthreads();                        // the tile before has been used up
+        locate_keys(where, table, j0, nk, TK, G, page_size);
+        __syncthreads();
         // (1) keys of all kv heads
         const int kv8 = dk / 8;
+#pragma unroll 2
         for (int i = tid; i < TK * G * kv8; i += kThreads) {
             const int jj = i / (G * kv8), rest = i - jj * (G * kv8), g = rest / kv8, c = rest - g * kv8;
+            const long long at = where[jj];
             uint4 v = make_uint4(0, 0, 0, 0);
-            if (jj < nk) {
-                const int pos = j0 + jj, lp = pos / page_size;
-                const int64_t page = table[lp];
-                if (page >= 0)
-                    v = *reinterpret_cast<const uint4*>(kcache + ((page * G + g) * page_size + (pos - lp * page_size)) * dk + c * 8);
-            }
+            if (at >= 0) v = *reinterpret_cast<const uint4*>(kcache + (at + (long long)g * page_size) * dk + c * 8);
             *reinterpret_cast<uint4*>(Ks + (size_t)jj * KP + g * dk + c * 8) = v;
         }
         __syncthreads();
@@ -377,15 +466,19 @@ attention_mixed_mma_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, i
         }
         __syncthreads();
         // (3) the values of the block's own kv heads, transposed, over the keys' place; the mixing and the mask
-        for (int i = tid; i < TK * n_own * dv; i += kThreads) {
-            const int e = i % dv, rest = i / dv, c = rest % n_own, jj = rest / n_own;
-            bf16 v = __float2bfloat16_rn(0.f);
-            if (jj < nk) {
-                const int pos = j0 + jj, lp = pos / page_size;
-                const int64_t page = table[lp];
-                if (page >= 0) v = vcache[((page * G + c_first + c) * page_size + (pos - lp * page_size)) * dv + e];
-            }
-            Vt[(size_t)(c * dv + e) * VP + jj] = v;
+        // (a thread takes eight channels of one key: neighbouring threads take neighbouring keys, so that the
+        // transposed stores of a warp fall into different banks)
+        const int dv8 = dv / 8;
+#pragma unroll 2
+        for (int i = tid; i < TK * n_own * dv8; i += kThreads) {
+            const int jj = i % TK, rest = i / TK, e8 = rest % dv8, c = rest / dv8;
+            const long long at = where[jj];
+            uint4 v = make_uint4(0, 0, 0, 0);
+            if (at >= 0) v = *reinterpret_cast<const uint4*>(vcache + (at + (long long)(c_first + c) * page_size) * dv + e8 * 8);
+            const bf16* h = reinterpret_cast<const bf16*>(&v);
+            bf16* o = Vt + (size_t)(c * dv + e8 * 8) * VP + jj;
+#pragma unroll
+            for (int u = 0; u < 8; u++) o[(size_t)u * VP] = h[u];
         }
         const int hb4 = (nh + 3) / 4;
         for (int it = tid; it < hb4 * kTile * TK; it += kThreads) {
@@ -496,15 +589,20 @@ inline MmaShape mma_shape(int H, int G, int dk, int dv) {
 // the caches' ([pages][G][page_size][dk] and [pages][G][page_size][dv]); mix float32 [H][H]; sinks float32 [H]
 // or NULL; request s brings rows q_start[s] .. q_start[s + 1] at positions start_pos[s] ...; tile_rows: rows of a
 // query tile (1 for single tokens), n_tiles: an upper bound of the tiles (sum over requests of ceil(rows / tile_rows)).
+// splits > 1 (tile_rows 1 and every request one token): the keys of a token are cut into that many ranges, one CTA each,
+// their results left in part_o float32 [tokens][splits][H * dv] and part_ml float32 [tokens][splits][H][2] and joined by a
+// second kernel.
 extern "C" int kllm_attention_mixed(void* out, const void* q, int64_t q_stride, const void* kcache, const void* vcache,
                                     const float* mix, const float* sinks, const int* q_start, const int* start_pos,
                                     const int* block_table, int max_blocks, int n_requests, int n_tiles, int tile_rows,
                                     int n_heads, int n_kv, int dk, int dv, int page_size, int window, float scale,
-                                    int dtype, void* stream) {
+                                    int splits, float* part_o, float* part_ml, int dtype, void* stream) {
     if (n_requests <= 0 || n_tiles <= 0) return 0;
     if (n_heads <= 0 || n_kv <= 0 || n_heads % n_kv || dk <= 0 || dv <= 0 || page_size <= 0)
         KLLM_FAIL("mixed attention: %d heads on %d kv heads of sizes %d, %d", n_heads, n_kv, dk, dv);
     if (tile_rows < 1 || tile_rows > kMaxTQ) KLLM_FAIL("mixed attention: tiles of %d rows (1 to %d)", tile_rows, kMaxTQ);
+    if (splits < 1 || (splits > 1 && (tile_rows != 1 || n_tiles != n_requests || !part_o || !part_ml)))
+        KLLM_FAIL("mixed attention: %d key ranges need single tokens and room for the ranges' results", splits);
     const size_t budget = 200 * 1024;
     Shape sh = {n_heads, n_kv, dk, dv, tile_rows, 32};
     while (sh.TK > 4 && smem_floats(sh) * sizeof(float) > budget) sh.TK /= 2;
@@ -519,7 +617,7 @@ extern "C" int kllm_attention_mixed(void* out, const void* q, int64_t q_stride, 
             cudaFuncSetAttribute(attention_mixed_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)budget);
             raised[0] = true;
         }
-        kllm_launch((attention_mixed_kernel<float>), dim3(n_tiles), dim3(kThreads), smem, s, (float*)out, (const float*)q,
+        kllm_launch((attention_mixed_kernel<float>), dim3(n_tiles, splits), dim3(kThreads), smem, s, (float*)out, part_o, part_ml, (const float*)q,
                     q_stride, (const float*)kcache, (const float*)vcache, mix, sinks, q_start, start_pos, block_table,
                     max_blocks, n_requests, sh, page_size, window, scale);
     } else if (dtype == KLLM_BF16) {
@@ -527,13 +625,30 @@ extern "C" int kllm_attention_mixed(void* out, const void* q, int64_t q_stride, 
             cudaFuncSetAttribute(attention_mixed_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)budget);
             raised[1] = true;
         }
-        kllm_launch((attention_mixed_kernel<bf16>), dim3(n_tiles), dim3(kThreads), smem, s, (bf16*)out, (const bf16*)q,
+        kllm_launch((attention_mixed_kernel<bf16>), dim3(n_tiles, splits), dim3(kThreads), smem, s, (bf16*)out, part_o, part_ml, (const bf16*)q,
                     q_stride, (const bf16*)kcache, (const bf16*)vcache, mix, sinks, q_start, start_pos, block_table,
                     max_blocks, n_requests, sh, page_size, window, scale);
     } else {
         KLLM_FAIL("mixed attention: unknown element type %d", dtype);
     }
+    if (splits > 1) {
+        cudaError_t e = cudaGetLastError();
+        if (e != cudaSuccess) KLLM_FAIL("mixed attention: %s", cudaGetErrorString(e));
+        if (dtype == KLLM_F32)
+            kllm_launch((attention_mixed_merge_kernel<float>), dim3(n_tiles), dim3(kThreads), 0, s, (float*)out, part_o, part_ml,
+                        splits, n_heads, dv);
+        else
+            kllm_launch((attention_mixed_merge_kernel<bf16>), dim3(n_tiles), dim3(kThreads), 0, s, (bf16*)out, part_o, part_ml,
+                        splits, n_heads, dv);
+    }
     KLLM_LAUNCH_STATUS();
+}
+
+// The keys of a tile on the CUDA-core form for these sizes and rows (what the cutting into ranges counts in).
+extern "C" int kllm_attention_mixed_tile_keys(int n_heads, int n_kv, int dk, int dv, int tile_rows) {
+    Shape sh = {n_heads, n_kv, dk, dv, tile_rows, 32};
+    while (sh.TK > 4 && smem_floats(sh) * sizeof(float) > 200 * 1024) sh.TK /= 2;
+    return sh.TK;
 }
 
 // The most rows a query tile of these sizes may have, at most 8: what fits shared memory beside a tile of 16

@@ -81,30 +81,79 @@ lightning_scan_kernel(float* __restrict__ o, int64_t o_stride, const float* __re
             if (j <= i) {
                 const float* qi = qs + i * qp;
                 const float* kj = ks + j * qp;
-                for (int d = 0; d < dk; d++) a = fmaf(qi[d], kj[d], a);
-                a *= pw[i - j];
+                float b = 0.f;
+                int d = 0;
+                for (; d + 1 < dk; d += 2) {
+                    a = fmaf(qi[d], kj[d], a);
+                    b = fmaf(qi[d + 1], kj[d + 1], b);
+                }
+                if (d < dk) a = fmaf(qi[d], kj[d], a);
+                a = (a + b) * pw[i - j];
             }
             A[i * (kChunk + 1) + j] = a;
         }
         __syncthreads();
-        // o_i[e] = w^(i+1) sum_d S[d][e] q_i[d] + sum_{j<=i} A[i][j] v_j[e]
-        for (int it = tid; it < n * ne; it += kThreads) {
-            const int i = it / ne, e = it - i * ne;
-            const float* qi = qs + i * qp;
-            float acc = 0.f;
-            for (int d = 0; d < dk; d++) acc = fmaf(S[d * sl + e], qi[d], acc);
-            acc *= pw[i + 1];
-            const float* Ai = A + i * (kChunk + 1);
-            for (int j = 0; j <= i; j++) acc = fmaf(Ai[j], vs[j * sl + e], acc);
-            o[(int64_t)(c0 + i) * o_stride + head * dv + e0 + e] = acc;
+        // o_i[e] = w^(i+1) sum_d S[d][e] q_i[d] + sum_{j<=i} A[i][j] v_j[e]: a thread takes four rows i of one channel e,
+        // so that a value of S or v read from shared memory serves four sums (A is zero above its diagonal)
+        const int ib = (n + 3) / 4;
+        for (int it = tid; it < ib * ne; it += kThreads) {
+            const int i0 = (it / ne) * 4, e = it - (it / ne) * ne;
+            const float* q0 = qs + i0 * qp;
+            const float* q1 = qs + min(i0 + 1, n - 1) * qp;
+            const float* q2 = qs + min(i0 + 2, n - 1) * qp;
+            const float* q3 = qs + min(i0 + 3, n - 1) * qp;
+            float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+#pragma unroll 4
+            for (int d = 0; d < dk; d++) {
+                const float sv = S[d * sl + e];
+                a0 = fmaf(sv, q0[d], a0);
+                a1 = fmaf(sv, q1[d], a1);
+                a2 = fmaf(sv, q2[d], a2);
+                a3 = fmaf(sv, q3[d], a3);
+            }
+            a0 *= pw[i0 + 1];
+            a1 *= pw[min(i0 + 2, kChunk)];
+            a2 *= pw[min(i0 + 3, kChunk)];
+            a3 *= pw[min(i0 + 4, kChunk)];
+            const float* A0 = A + i0 * (kChunk + 1);
+            const float* A1 = A + min(i0 + 1, n - 1) * (kChunk + 1);
+            const float* A2 = A + min(i0 + 2, n - 1) * (kChunk + 1);
+            const float* A3 = A + min(i0 + 3, n - 1) * (kChunk + 1);
+            const int jn = min(n, i0 + 4);
+#pragma unroll 4
+            for (int j = 0; j < jn; j++) {
+                const float vv = vs[j * sl + e];
+                a0 = fmaf(A0[j], vv, a0);
+                a1 = fmaf(A1[j], vv, a1);
+                a2 = fmaf(A2[j], vv, a2);
+                a3 = fmaf(A3[j], vv, a3);
+            }
+            float* orow = o + (int64_t)(c0 + i0) * o_stride + head * dv + e0 + e;
+            orow[0] = a0;
+            if (i0 + 1 < n) orow[o_stride] = a1;
+            if (i0 + 2 < n) orow[2 * o_stride] = a2;
+            if (i0 + 3 < n) orow[3 * o_stride] = a3;
         }
         __syncthreads();
-        // S[d][e] = w^n S[d][e] + sum_j w^(n-1-j) k_j[d] v_j[e]
-        for (int it = tid; it < dk * ne; it += kThreads) {
-            const int d = it / ne, e = it - d * ne;
-            float acc = S[d * sl + e] * pw[n];
-            for (int j = 0; j < n; j++) acc = fmaf(ks[j * qp + d] * pw[n - 1 - j], vs[j * sl + e], acc);
-            S[d * sl + e] = acc;
+        // S[d][e] = w^n S[d][e] + sum_j w^(n-1-j) k_j[d] v_j[e]: a thread takes four key channels d of one channel e
+        const int db = (dk + 3) / 4;
+        for (int it = tid; it < db * ne; it += kThreads) {
+            const int d0 = (it / ne) * 4, e = it - (it / ne) * ne;
+            const int d1 = min(d0 + 1, dk - 1), d2 = min(d0 + 2, dk - 1), d3 = min(d0 + 3, dk - 1);
+            float a0 = S[d0 * sl + e] * pw[n], a1 = S[d1 * sl + e] * pw[n], a2 = S[d2 * sl + e] * pw[n], a3 = S[d3 * sl + e] * pw[n];
+#pragma unroll 4
+            for (int j = 0; j < n; j++) {
+                const float vv = vs[j * sl + e] * pw[n - 1 - j];
+                const float* kj = ks + j * qp;
+                a0 = fmaf(kj[d0], vv, a0);
+                a1 = fmaf(kj[d1], vv, a1);
+                a2 = fmaf(kj[d2], vv, a2);
+                a3 = fmaf(kj[d3], vv, a3);
+            }
+            S[d0 * sl + e] = a0;
+            if (d0 + 1 < dk) S[(d0 + 1) * sl + e] = a1;
+            if (d0 + 2 < dk) S[(d0 + 2) * sl + e] = a2;
+            if (d0 + 3 < dk) S[(d0 + 3) * sl + e] = a3;
         }
     }
     __syncthreads();
@@ -157,6 +206,9 @@ extern "C" int kllm_lightning_scan(float* o, int64_t o_stride, const float* q, i
     int sl = dv < 64 ? dv : 64;
     while (sl > 1 && scan_smem(dk, sl) > 200 * 1024) sl = (sl + 1) / 2;
     if (scan_smem(dk, sl) > 200 * 1024) KLLM_FAIL("lightning scan: a head of %d key channels does not fit shared memory", dk);
+    // a launch of few (head, request) pairs gets narrower slices, down to 16 channels: more CTAs, each repeating the
+    // chunk's small q k^T product
+    while (sl > 16 && (int64_t)heads * n_requests * ((dv + sl - 1) / sl) < 148) sl = (sl + 1) / 2;
     const int slices = (dv + sl - 1) / sl;
     const size_t smem = scan_smem(dk, sl);
     static size_t allowed = 48 * 1024;

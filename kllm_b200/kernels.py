@@ -1499,11 +1499,27 @@ def attention_mixed(out: torch.Tensor, q: torch.Tensor, kcache: torch.Tensor, vc
     if ctx.all_single:
         rows = 1
     tiles = ctx.n_requests if rows == 1 else ctx.n_tokens // rows + ctx.n_requests
+    # single tokens: the keys a token sees are cut into ranges of whole key tiles, one CTA each, as many as fill the
+    # SMs once, at least four tiles a range; a second kernel joins them in range order
+    splits, part_o, part_ml = 1, None, None
+    if ctx.all_single:
+        bound = ctx.split_bound or ctx.max_ctx
+        if window:
+            bound = min(bound, int(window))
+        tile_keys = int(lib.kllm_attention_mixed_tile_keys(n_heads, n_kv, head_dim, v_head_dim, 1))
+        splits = max(1, min(-(-bound // (4 * tile_keys)), sm_count() // max(1, ctx.n_requests), 32))
+        if splits > 1:
+            part_o = torch.empty((n, splits, n_heads * v_head_dim), dtype=torch.float32, device=q.device)
+            part_ml = torch.empty((n, splits, n_heads, 2), dtype=torch.float32, device=q.device)
     rc = lib.kllm_attention_mixed(_p(out), _p(q), ctypes.c_int64(q.stride(0)), _p(kcache), _p(vcache), _p(mix), _p(sinks),
                                   _p(ctx.q_start), _p(ctx.start_pos), _p(block_table), block_table.shape[1],
                                   ctx.n_requests, int(tiles), int(rows), n_heads, n_kv, head_dim, v_head_dim, page_size,
-                                  int(window or 0), ctypes.c_float(scale), dtype_code(q.dtype), _stream())
+                                  int(window or 0), ctypes.c_float(scale), int(splits), _p(part_o), _p(part_ml),
+                                  dtype_code(q.dtype), _stream())
     _check(lib, "attention_mixed", rc)
+    if splits > 1:
+        global launches
+        launches += 1           # the merging kernel
 
 
 # ---- routed experts (csrc/moe.cu) ------------------------------------------------------
