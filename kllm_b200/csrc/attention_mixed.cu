@@ -30,7 +30,7 @@ KLLM_EXPORT_LAST_ERROR(attention_mixed)
 namespace {
 
 constexpr int kThreads = 256;
-constexpr int kMaxPer = 16;     // query heads on a kv head that one thread scores together
+constexpr int kMaxPer = 4;      // query heads on a kv head that one thread scores together (a larger group in turns)
 constexpr int kMaxTQ = 8;       // rows of a tile
 
 struct Shape {
@@ -241,7 +241,24 @@ attention_mixed_kernel(T* __restrict__ out, float* __restrict__ part_o, float* _
             }
         }
         __syncthreads();
-        // (5) output: a thread per (head, value channel), all rows of the tile
+        // (5) output: a thread per (head, value channel), all rows of the tile (a single token's one row on its own:
+        // the general form would issue the other seven rows' instructions with their predicates off)
+        if (nq == 1) {
+            for (int it = tid; it < H * dv; it += kThreads) {
+                const int h = it / dv, e = it - h * dv;
+                const float* vr = kt + (h / per) * dv + e;
+                const float* pw = pr + (size_t)h * TQ * TK;
+                float a = 0.f, b = 0.f;
+                int jj = 0;
+                for (; jj + 1 < nk; jj += 2) {
+                    a = fmaf(pw[jj], vr[jj * kp], a);
+                    b = fmaf(pw[jj + 1], vr[(jj + 1) * kp], b);
+                }
+                if (jj < nk) a = fmaf(pw[jj], vr[jj * kp], a);
+                acc[it] = acc[it] * cr[h * TQ] + (a + b);
+            }
+            continue;
+        }
         for (int it = tid; it < H * dv; it += kThreads) {
             const int h = it / dv, e = it - h * dv;
             const float* vr = kt + (h / per) * dv + e;
@@ -310,13 +327,14 @@ attention_mixed_merge_kernel(T* __restrict__ out, const float* __restrict__ part
 // The same sums with the two products on the tensor cores (mma.sync m16n8k16, bfloat16 operands, float32
 // accumulators): a CTA takes a tile of 16 query rows and a block of HB output heads.  Per key tile it forms the raw
 // scores of ALL heads (every output head needs them all), mixes them for its own heads in float32 on the CUDA
-// cores, and keeps the output of its own heads in registers: 16 x HB x dv float32 values spread over the eight
+// cores, and keeps the output of its own heads in registers: 16 x HB x dv float32 values spread over the sixteen
 // warps as m16n8 accumulator tiles.  The weights stay float32 until they meet the values: they enter the second
 // product as two bfloat16 terms (the weight rounded, and what the rounding left), which keeps 16 bits of mantissa.
 // Shared memory: the Q tile of all heads, the K tile of all kv heads (its place is reused for the transposed V tile
 // of the block's own kv heads), the raw scores (their place is reused for the two-term weights), the mixed scores.
 constexpr int kTile = 16;       // query rows of a tile
-constexpr int kFrags = 16;      // m16n8 accumulator tiles a warp may own: HB * dv / 8 <= 8 * kFrags
+constexpr int kMmaThreads = 512; // sixteen warps: four a scheduler, so that one warp's waits are another's work
+constexpr int kFrags = 8;       // m16n8 accumulator tiles a warp may own: HB * dv / 8 <= 16 * kFrags
 
 struct MmaShape {
     int H, G, dk, dv, HB, TK;
@@ -358,7 +376,7 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1
                  : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-__global__ void __launch_bounds__(kThreads)
+__global__ void __launch_bounds__(kMmaThreads)
 attention_mixed_mma_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, int64_t q_stride,
                            const bf16* __restrict__ kcache, const bf16* __restrict__ vcache,
                            const float* __restrict__ mix, const float* __restrict__ sinks,
@@ -389,7 +407,7 @@ attention_mixed_mma_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, i
     const int nh = min(HB, H - h0);
     const int c_first = h0 / per;                               // first kv head of the block's own heads
     const int n_own = (h0 + nh - 1) / per - c_first + 1;
-    for (int i = tid; i < nh * H; i += kThreads) ms[i] = mix[(size_t)(h0 + i / H) * H + i % H] * scale;
+    for (int i = tid; i < nh * H; i += kMmaThreads) ms[i] = mix[(size_t)(h0 + i / H) * H + i % H] * scale;
     griddep_wait();
     griddep_launch();
     int req = 0, tile = blockIdx.x;
@@ -408,13 +426,13 @@ attention_mixed_mma_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, i
 
     // the Q tile of all heads, 16 bytes at a time; rows past the portion's end are zero
     const int qv = H * dk / 8;
-    for (int i = tid; i < kTile * qv; i += kThreads) {
+    for (int i = tid; i < kTile * qv; i += kMmaThreads) {
         const int r = i / qv, c = i - r * qv;
         uint4 v = make_uint4(0, 0, 0, 0);
         if (r < nq) v = *reinterpret_cast<const uint4*>(q + (int64_t)(row0 + r) * q_stride + c * 8);
         *reinterpret_cast<uint4*>(Qs + (size_t)r * QP + c * 8) = v;
     }
-    for (int i = tid; i < HB * kTile; i += kThreads) {
+    for (int i = tid; i < HB * kTile; i += kMmaThreads) {
         const int h = h0 + i / kTile;
         mx[i] = (sinks && h < H) ? sinks[h] : -INFINITY;
         dn[i] = sinks ? 1.f : 0.f;
@@ -433,7 +451,7 @@ attention_mixed_mma_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, i
         // (1) keys of all kv heads
         const int kv8 = dk / 8;
 #pragma unroll 2
-        for (int i = tid; i < TK * G * kv8; i += kThreads) {
+        for (int i = tid; i < TK * G * kv8; i += kMmaThreads) {
             const int jj = i / (G * kv8), rest = i - jj * (G * kv8), g = rest / kv8, c = rest - g * kv8;
             const long long at = where[jj];
             uint4 v = make_uint4(0, 0, 0, 0);
@@ -442,7 +460,7 @@ attention_mixed_mma_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, i
         }
         __syncthreads();
         // (2) raw scores: a warp takes whole heads; A = the head's Q rows, B = its kv head's keys
-        for (int g = warp; g < H; g += kThreads / 32) {
+        for (int g = warp; g < H; g += kMmaThreads / 32) {
             float c[4][4];
 #pragma unroll
             for (int nt = 0; nt < 4; nt++) c[nt][0] = c[nt][1] = c[nt][2] = c[nt][3] = 0.f;
@@ -470,7 +488,7 @@ attention_mixed_mma_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, i
         // transposed stores of a warp fall into different banks)
         const int dv8 = dv / 8;
 #pragma unroll 2
-        for (int i = tid; i < TK * n_own * dv8; i += kThreads) {
+        for (int i = tid; i < TK * n_own * dv8; i += kMmaThreads) {
             const int jj = i % TK, rest = i / TK, e8 = rest % dv8, c = rest / dv8;
             const long long at = where[jj];
             uint4 v = make_uint4(0, 0, 0, 0);
@@ -481,7 +499,7 @@ attention_mixed_mma_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, i
             for (int u = 0; u < 8; u++) o[(size_t)u * VP] = h[u];
         }
         const int hb4 = (nh + 3) / 4;
-        for (int it = tid; it < hb4 * kTile * TK; it += kThreads) {
+        for (int it = tid; it < hb4 * kTile * TK; it += kMmaThreads) {
             const int jj = it % TK, i = (it / TK) % kTile, b0 = (it / (TK * kTile)) * 4;
             const int pos = j0 + jj, pi = p0 + i;
             const bool visible = jj < nk && i < nq && pos <= pi && (window <= 0 || pi - pos < window);
@@ -508,19 +526,23 @@ attention_mixed_mma_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, i
         }
         __syncthreads();
         // (4) one warp per (head, row): maximum, two-term weights, denominator
-        for (int rw = warp; rw < nh * kTile; rw += kThreads / 32) {
-            const float s = lane < TK ? mixed[(size_t)rw * RP + lane] : -INFINITY;
+        // (a warp takes 32 / TK rows at a time, TK lanes each: TK is 16 or 32 and the rows' count is a multiple of 16)
+        const int rpw = 32 / TK, sub = lane / TK, jl = lane - sub * TK;
+        for (int r0 = warp * rpw; r0 < nh * kTile; r0 += (kMmaThreads / 32) * rpw) {
+            const int rw = r0 + sub;
+            const float s = mixed[(size_t)rw * RP + jl];
             const float m_old = mx[rw];
-            const float m_new = fmaxf(m_old, warp_max(s));
+            float top = s;
+            for (int o = TK >> 1; o > 0; o >>= 1) top = fmaxf(top, __shfl_xor_sync(0xffffffffu, top, o));
+            const float m_new = fmaxf(m_old, top);
             const float w = (s == -INFINITY) ? 0.f : expf(s - m_new);
             const float c = (m_old == -INFINITY) ? 0.f : expf(m_old - m_new);
-            const float sum = warp_sum(w);
-            if (lane < TK) {
-                const bf16 wh = __float2bfloat16_rn(w);
-                Ph[(size_t)rw * PP + lane] = wh;
-                Pl[(size_t)rw * PP + lane] = __float2bfloat16_rn(w - __bfloat162float(wh));
-            }
-            if (lane == 0) {
+            float sum = w;
+            for (int o = TK >> 1; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+            const bf16 wh = __float2bfloat16_rn(w);
+            Ph[(size_t)rw * PP + jl] = wh;
+            Pl[(size_t)rw * PP + jl] = __float2bfloat16_rn(w - __bfloat162float(wh));
+            if (jl == 0) {
                 mx[rw] = m_new;
                 dn[rw] = dn[rw] * c + sum;
                 cr[rw] = c;
@@ -530,7 +552,7 @@ attention_mixed_mma_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, i
         // (5) the output tiles this warp owns: tile t = (head of the block, eight value channels)
 #pragma unroll
         for (int f = 0; f < kFrags; f++) {
-            const int t = warp + f * (kThreads / 32);
+            const int t = warp + f * (kMmaThreads / 32);
             if (t < n_tiles) {
                 const int hb = t / ntv, nt = t - hb * ntv;
                 const float c_lo = cr[hb * kTile + fr], c_hi = cr[hb * kTile + fr + 8];
@@ -549,7 +571,7 @@ attention_mixed_mma_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, i
     __syncthreads();
 #pragma unroll
     for (int f = 0; f < kFrags; f++) {
-        const int t = warp + f * (kThreads / 32);
+        const int t = warp + f * (kMmaThreads / 32);
         if (t < n_tiles) {
             const int hb = t / ntv, nt = t - hb * ntv;
             const int col = (h0 + hb) * dv + nt * 8 + fc;
@@ -571,8 +593,8 @@ attention_mixed_mma_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, i
 // The block of heads and the key tile of the tensor-core form for these sizes; HB 0: the form does not take them.
 inline MmaShape mma_shape(int H, int G, int dk, int dv) {
     MmaShape s = {H, G, dk, dv, 0, 0};
-    if (dk % 16 || dv % 16 || dv > 8 * kFrags * 8) return s;
-    int hb = 8 * kFrags * 8 / dv;
+    if (dk % 16 || dv % 16 || dv > (kMmaThreads / 32) * kFrags * 8) return s;
+    int hb = (kMmaThreads / 32) * kFrags * 8 / dv;
     if (hb > H) hb = H;
     for (int tk = 32; tk >= 16; tk /= 2) {
         s.HB = hb;
@@ -688,7 +710,7 @@ extern "C" int kllm_attention_mixed_mma(void* out, const void* q, int64_t q_stri
         raised = true;
     }
     const int groups = (n_heads + sh.HB - 1) / sh.HB;
-    kllm_launch((attention_mixed_mma_kernel), dim3(n_tiles, groups), dim3(kThreads), smem, (cudaStream_t)stream, (bf16*)out,
+    kllm_launch((attention_mixed_mma_kernel), dim3(n_tiles, groups), dim3(kMmaThreads), smem, (cudaStream_t)stream, (bf16*)out,
                 (const bf16*)q, q_stride, (const bf16*)kcache, (const bf16*)vcache, mix, sinks, q_start, start_pos, block_table,
                 max_blocks, n_requests, sh, page_size, window, scale);
     KLLM_LAUNCH_STATUS();
