@@ -1428,6 +1428,20 @@ def lightning_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, decay: tor
     _i32(ctx.q_start, "q_start"); _i32(ctx.state_slots, "state_slots")
     o = torch.empty((q.shape[0], heads * dv), dtype=torch.float32, device=q.device)
     lib = load_library("lightning")
+    if not ctx.all_single:
+        # portions: the chunks' own sums in parallel, then the state's walk (two kernels; see csrc/lightning.cu)
+        n = q.shape[0]
+        work = torch.empty((3, n, heads * max(dk, dv)), dtype=torch.float32, device=q.device)
+        rc = lib.kllm_lightning_scan_portions(_p(o), ctypes.c_int64(o.stride(0)), _p(q), ctypes.c_int64(q.stride(0)), _p(k),
+                                              ctypes.c_int64(k.stride(0)), _p(v), ctypes.c_int64(v.stride(0)), _p(decay),
+                                              _p(state), ctypes.c_int64(state.stride(0)), _p(ctx.q_start),
+                                              _p(ctx.state_slots), n, ctx.n_requests, n // 32 + ctx.n_requests, heads, dk,
+                                              dv, _p(work[0]), _p(work[1]), _p(work[2]), _stream())
+        if rc != -3:
+            _check(lib, "lightning", rc)
+            global launches
+            launches += 1
+            return o
     rc = lib.kllm_lightning_scan(_p(o), ctypes.c_int64(o.stride(0)), _p(q), ctypes.c_int64(q.stride(0)), _p(k),
                                  ctypes.c_int64(k.stride(0)), _p(v), ctypes.c_int64(v.stride(0)), _p(decay), _p(state),
                                  ctypes.c_int64(state.stride(0)), _p(ctx.q_start), _p(ctx.state_slots), q.shape[0],
@@ -1500,14 +1514,14 @@ def attention_mixed(out: torch.Tensor, q: torch.Tensor, kcache: torch.Tensor, vc
         rows = 1
     tiles = ctx.n_requests if rows == 1 else ctx.n_tokens // rows + ctx.n_requests
     # single tokens: the keys a token sees are cut into ranges of whole key tiles, one CTA each, as many as fill the
-    # SMs once, at least four tiles a range; a second kernel joins them in range order
+    # SMs once, at least two tiles a range; a second kernel joins them in range order
     splits, part_o, part_ml = 1, None, None
     if ctx.all_single:
         bound = ctx.split_bound or ctx.max_ctx
         if window:
             bound = min(bound, int(window))
         tile_keys = int(lib.kllm_attention_mixed_tile_keys(n_heads, n_kv, head_dim, v_head_dim, 1))
-        splits = max(1, min(-(-bound // (4 * tile_keys)), sm_count() // max(1, ctx.n_requests), 32))
+        splits = max(1, min(-(-bound // (2 * tile_keys)), sm_count() // max(1, ctx.n_requests), 32))
         if splits > 1:
             part_o = torch.empty((n, splits, n_heads * v_head_dim), dtype=torch.float32, device=q.device)
             part_ml = torch.empty((n, splits, n_heads, 2), dtype=torch.float32, device=q.device)
