@@ -590,6 +590,308 @@ attention_mixed_mma_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, i
     }
 }
 
+// ---- the tensor-core form over a thread-block cluster ------------------------------------------------------
+// The CTAs that share a tile of 16 query rows form a cluster, one CTA per block of HB heads (H = NB * HB, NB <= 8).
+// A CTA computes the raw scores of ITS heads only, against the keys of its own kv heads, and leaves them in its shared
+// memory; after a cluster barrier every CTA mixes the scores of all heads for its own heads, reading the other
+// blocks' raw scores from their shared memory (distributed shared memory), and goes on alone: softmax, weights in
+// two bfloat16 terms, second product with the values of its own kv heads.  No score is computed twice, no CTA holds
+// more than its own heads' queries, keys and values, and several CTAs fit an SM.  Two cluster barriers per key tile:
+// before the raw scores are overwritten (all blocks have mixed the tile before) and after they are written.
+constexpr int kClThreads = 256;
+constexpr int kClFrags = 8;     // m16n8 accumulator tiles a warp may own: HB * dv / 8 <= 8 * kClFrags
+constexpr int kClTK = 32;       // keys of a tile
+
+struct ClShape {
+    int H, G, dk, dv, HB, NB, KV;   // KV: the most kv heads a block's heads lie on
+};
+
+struct ClLayout {
+    size_t q, k, raw, mixed, p, stats, mix, where, total;
+};
+
+__host__ __device__ inline ClLayout cl_layout(const ClShape& s) {
+    ClLayout L;
+    size_t o = 0;
+    L.q = o;      o += (size_t)kTile * (s.HB * s.dk + 8) * 2;
+    const size_t ktile = (size_t)kClTK * (s.KV * s.dk + 8) * 2;
+    const size_t vtile = (size_t)s.KV * s.dv * (kClTK + 8) * 2;
+    L.k = o;      o += (ktile > vtile ? ktile : vtile);
+    L.raw = o;    o += (size_t)s.HB * kTile * (kClTK + 4) * 4;
+    L.mixed = o;  o += (size_t)s.HB * kTile * (kClTK + 4) * 4;
+    L.p = o;      o += 2 * (size_t)s.HB * kTile * (kClTK + 8) * 2;
+    L.stats = o;  o += 3 * (size_t)s.HB * kTile * 4;
+    L.mix = o;    o += (size_t)((s.HB + 3) / 4) * s.H * 4 * 4;        // [blocks of four heads][H][4]
+    L.where = o;  o += (size_t)kClTK * 8;
+    L.total = (o + 15) / 16 * 16;
+    return L;
+}
+
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;\n" ::: "memory");
+}
+
+// The address, in this CTA's shared window, of `p` as it lies in the shared memory of the cluster's CTA `rank`.
+__device__ __forceinline__ const float* peer_shared(const float* p, unsigned rank) {
+    uint64_t out;
+    asm volatile("mapa.u64 %0, %1, %2;\n" : "=l"(out) : "l"((uint64_t)p), "r"(rank));
+    return reinterpret_cast<const float*>(out);
+}
+
+__global__ void __launch_bounds__(kClThreads, 3)
+attention_mixed_cluster_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, int64_t q_stride,
+                               const bf16* __restrict__ kcache, const bf16* __restrict__ vcache,
+                               const float* __restrict__ mix, const float* __restrict__ sinks,
+                               const int* __restrict__ q_start, const int* __restrict__ start_pos,
+                               const int* __restrict__ block_table, int max_blocks, int n_requests, ClShape sh,
+                               int page_size, int window, float scale) {
+    extern __shared__ __align__(16) unsigned char smraw[];
+    const int H = sh.H, G = sh.G, dk = sh.dk, dv = sh.dv, HB = sh.HB, NB = sh.NB;
+    constexpr int TK = kClTK;
+    const int per = H / G;
+    const ClLayout L = cl_layout(sh);
+    const int QP = HB * dk + 8, KP = sh.KV * dk + 8, VP = TK + 8, RP = TK + 4, PP = TK + 8;
+    bf16* Qs = reinterpret_cast<bf16*>(smraw + L.q);            // [16][QP]: the block's own heads
+    bf16* Ks = reinterpret_cast<bf16*>(smraw + L.k);            // [TK][KP]: the block's own kv heads
+    bf16* Vt = Ks;                                              // [own kv heads * dv][VP], after the scores
+    float* raw = reinterpret_cast<float*>(smraw + L.raw);       // [HB][16][RP]: read by the whole cluster
+    float* mixed = reinterpret_cast<float*>(smraw + L.mixed);   // [HB][16][RP]
+    bf16* Ph = reinterpret_cast<bf16*>(smraw + L.p);            // [HB][16][PP]
+    bf16* Pl = Ph + (size_t)HB * kTile * PP;
+    float* mx = reinterpret_cast<float*>(smraw + L.stats);
+    float* dn = mx + HB * kTile;
+    float* cr = dn + HB * kTile;
+    float* ms = reinterpret_cast<float*>(smraw + L.mix);        // [blocks of four own heads][H][4], times scale
+    long long* where = reinterpret_cast<long long*>(smraw + L.where);
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int fr = lane >> 2, fc = (lane & 3) * 2;
+
+    const int rank = blockIdx.y;                                // the cluster spans the grid's y: the rank in it
+    const int h0 = rank * HB;
+    const int c_first = h0 / per;
+    const int n_own = (h0 + HB - 1) / per - c_first + 1;
+    for (int i = tid; i < ((HB + 3) / 4) * H * 4; i += kClThreads) {
+        const int u = i & 3, g = (i >> 2) % H, hb = (i >> 2) / H * 4 + u;     // weight of head g in own head hb
+        ms[i] = hb < HB ? mix[(size_t)(h0 + hb) * H + g] * scale : 0.f;
+    }
+    griddep_wait();
+    griddep_launch();
+    int req = 0, tile = blockIdx.x;
+    for (; req < n_requests; req++) {
+        const int tiles = (q_start[req + 1] - q_start[req] + kTile - 1) / kTile;
+        if (tile < tiles) break;
+        tile -= tiles;
+    }
+    if (req >= n_requests) return;                              // the same for every CTA of the cluster
+    const int row0 = q_start[req] + tile * kTile;
+    const int nq = min(kTile, q_start[req + 1] - row0);
+    const int p0 = start_pos[req] + tile * kTile;
+    const int hi = p0 + nq - 1;
+    const int lo = window > 0 ? max(0, p0 - window + 1) : 0;
+    const int* table = block_table + (int64_t)req * max_blocks;
+
+    const int qv = HB * dk / 8;
+    for (int i = tid; i < kTile * qv; i += kClThreads) {
+        const int r = i / qv, c = i - r * qv;
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (r < nq) v = *reinterpret_cast<const uint4*>(q + (int64_t)(row0 + r) * q_stride + (size_t)h0 * dk + c * 8);
+        *reinterpret_cast<uint4*>(Qs + (size_t)r * QP + c * 8) = v;
+    }
+    for (int i = tid; i < HB * kTile; i += kClThreads) {
+        mx[i] = sinks ? sinks[h0 + i / kTile] : -INFINITY;
+        dn[i] = sinks ? 1.f : 0.f;
+    }
+    float acc[kClFrags][4];
+#pragma unroll
+    for (int f = 0; f < kClFrags; f++) acc[f][0] = acc[f][1] = acc[f][2] = acc[f][3] = 0.f;
+    const int ntv = dv / 8;
+    const int n_tiles = HB * ntv;
+    const float* peer_raw[8];
+#pragma unroll
+    for (int r = 0; r < 8; r++) peer_raw[r] = peer_shared(raw, r < NB ? r : 0);
+
+    for (int j0 = lo; j0 <= hi; j0 += TK) {
+        const int nk = min(TK, hi - j0 + 1);
+        cluster_sync_all();                     // every block has mixed the tile before: raw may be overwritten
+        locate_keys(where, table, j0, nk, TK, G, page_size);
+        __syncthreads();
+        // (1) keys of the block's own kv heads
+        const int kv8 = dk / 8;
+#pragma unroll 2
+        for (int i = tid; i < TK * n_own * kv8; i += kClThreads) {
+            const int jj = i / (n_own * kv8), rest = i - jj * (n_own * kv8), c = rest / kv8, d8 = rest - c * kv8;
+            const long long at = where[jj];
+            uint4 v = make_uint4(0, 0, 0, 0);
+            if (at >= 0) v = *reinterpret_cast<const uint4*>(kcache + (at + (long long)(c_first + c) * page_size) * dk + d8 * 8);
+            *reinterpret_cast<uint4*>(Ks + (size_t)jj * KP + c * dk + d8 * 8) = v;
+        }
+        __syncthreads();
+        // (2) raw scores of the block's own heads: a unit is (head, eight keys)
+        for (int u = warp; u < HB * (TK / 8); u += kClThreads / 32) {
+            const int hb = u / (TK / 8), nt = u - hb * (TK / 8);
+            float c[4] = {0.f, 0.f, 0.f, 0.f};
+            const bf16* qa = Qs + (size_t)fr * QP + hb * dk + fc;
+            const bf16* kb = Ks + (size_t)(nt * 8 + fr) * KP + ((h0 + hb) / per - c_first) * dk + fc;
+#pragma unroll 4
+            for (int k0 = 0; k0 < dk; k0 += 16)
+                mma_bf16(c, ld32(qa + k0), ld32(qa + 8 * QP + k0), ld32(qa + k0 + 8), ld32(qa + 8 * QP + k0 + 8), ld32(kb + k0),
+                         ld32(kb + k0 + 8));
+            float* rg = raw + (size_t)hb * kTile * RP + nt * 8 + fc;
+            rg[fr * RP] = c[0];
+            rg[fr * RP + 1] = c[1];
+            rg[(fr + 8) * RP] = c[2];
+            rg[(fr + 8) * RP + 1] = c[3];
+        }
+        cluster_sync_all();                     // the raw scores of all blocks are written
+        // (3) the values of the block's own kv heads, transposed, over the keys' place; the mixing and the mask
+        const int dv8 = dv / 8;
+#pragma unroll 2
+        for (int i = tid; i < TK * n_own * dv8; i += kClThreads) {
+            const int jj = i % TK, rest = i / TK, e8 = rest % dv8, c = rest / dv8;
+            const long long at = where[jj];
+            uint4 v = make_uint4(0, 0, 0, 0);
+            if (at >= 0) v = *reinterpret_cast<const uint4*>(vcache + (at + (long long)(c_first + c) * page_size) * dv + e8 * 8);
+            const bf16* h = reinterpret_cast<const bf16*>(&v);
+            bf16* o = Vt + (size_t)(c * dv + e8 * 8) * VP + jj;
+#pragma unroll
+            for (int u = 0; u < 8; u++) o[(size_t)u * VP] = h[u];
+        }
+        // (a thread mixes two neighbouring keys of one row for four own heads: one 8-byte read of a raw score pair and
+        // one 16-byte read of the four heads' weights serve eight sums)
+        const int hb4 = (HB + 3) / 4;
+        for (int it = tid; it < hb4 * kTile * (TK / 2); it += kClThreads) {
+            const int j2 = it % (TK / 2), i = (it / (TK / 2)) % kTile, b4 = it / ((TK / 2) * kTile);
+            const int b0 = b4 * 4;
+            float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f, c0 = 0.f, c1 = 0.f, c2 = 0.f, c3 = 0.f;
+            if (i < nq) {
+                const int off = i * RP + 2 * j2;
+                const float4* mw = reinterpret_cast<const float4*>(ms) + (size_t)b4 * H;
+#pragma unroll
+                for (int r = 0; r < 8; r++) {
+                    if (r < NB) {
+                        const float* rr = peer_raw[r] + off;
+#pragma unroll 4
+                        for (int gg = 0; gg < HB; gg++) {
+                            const float2 x = *reinterpret_cast<const float2*>(rr + (size_t)gg * kTile * RP);
+                            const float4 m = mw[r * HB + gg];
+                            a0 = fmaf(m.x, x.x, a0); c0 = fmaf(m.x, x.y, c0);
+                            a1 = fmaf(m.y, x.x, a1); c1 = fmaf(m.y, x.y, c1);
+                            a2 = fmaf(m.z, x.x, a2); c2 = fmaf(m.z, x.y, c2);
+                            a3 = fmaf(m.w, x.x, a3); c3 = fmaf(m.w, x.y, c3);
+                        }
+                    }
+                }
+            }
+            const int pi = p0 + i, pos = j0 + 2 * j2;
+            const bool v0 = 2 * j2 < nk && i < nq && pos <= pi && (window <= 0 || pi - pos < window);
+            const bool v1 = 2 * j2 + 1 < nk && i < nq && pos + 1 <= pi && (window <= 0 || pi - pos - 1 < window);
+            float* dst = mixed + (size_t)(b0 * kTile + i) * RP + 2 * j2;
+            *reinterpret_cast<float2*>(dst) = make_float2(v0 ? a0 : -INFINITY, v1 ? c0 : -INFINITY);
+            if (b0 + 1 < HB) *reinterpret_cast<float2*>(dst + kTile * RP) = make_float2(v0 ? a1 : -INFINITY, v1 ? c1 : -INFINITY);
+            if (b0 + 2 < HB) *reinterpret_cast<float2*>(dst + 2 * kTile * RP) = make_float2(v0 ? a2 : -INFINITY, v1 ? c2 : -INFINITY);
+            if (b0 + 3 < HB) *reinterpret_cast<float2*>(dst + 3 * kTile * RP) = make_float2(v0 ? a3 : -INFINITY, v1 ? c3 : -INFINITY);
+        }
+        __syncthreads();
+        // (4) four lanes per (head, row), eight keys each: maximum, two-term weights, denominator
+        for (int r0 = warp * 8; r0 < HB * kTile; r0 += (kClThreads / 32) * 8) {
+            const int rw = r0 + (lane >> 2), part = lane & 3;
+            const float* src = mixed + (size_t)rw * RP + part * 8;
+            const float m_old = mx[rw], d_old = dn[rw];
+            float sc[8];
+            float top = -INFINITY;
+#pragma unroll
+            for (int t = 0; t < 8; t++) {
+                sc[t] = src[t];
+                top = fmaxf(top, sc[t]);
+            }
+            top = fmaxf(top, __shfl_xor_sync(0xffffffffu, top, 1));
+            top = fmaxf(top, __shfl_xor_sync(0xffffffffu, top, 2));
+            const float m_new = fmaxf(m_old, top);
+            float sum = 0.f;
+            uint32_t* ph = reinterpret_cast<uint32_t*>(Ph + (size_t)rw * PP + part * 8);
+            uint32_t* pl = reinterpret_cast<uint32_t*>(Pl + (size_t)rw * PP + part * 8);
+#pragma unroll
+            for (int t = 0; t < 8; t += 2) {
+                const float w0 = (sc[t] == -INFINITY) ? 0.f : expf(sc[t] - m_new);
+                const float w1 = (sc[t + 1] == -INFINITY) ? 0.f : expf(sc[t + 1] - m_new);
+                sum += w0 + w1;
+                const __nv_bfloat162 hi = __floats2bfloat162_rn(w0, w1);
+                const float2 back = __bfloat1622float2(hi);
+                const __nv_bfloat162 lo = __floats2bfloat162_rn(w0 - back.x, w1 - back.y);
+                ph[t >> 1] = *reinterpret_cast<const uint32_t*>(&hi);
+                pl[t >> 1] = *reinterpret_cast<const uint32_t*>(&lo);
+            }
+            sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+            sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+            if (part == 0) {
+                const float c = (m_old == -INFINITY) ? 0.f : expf(m_old - m_new);
+                mx[rw] = m_new;
+                dn[rw] = d_old * c + sum;
+                cr[rw] = c;
+            }
+        }
+        __syncthreads();
+        // (5) the output tiles this warp owns
+#pragma unroll
+        for (int f = 0; f < kClFrags; f++) {
+            const int t = warp + f * (kClThreads / 32);
+            if (t < n_tiles) {
+                const int hb = t / ntv, nt = t - hb * ntv;
+                const float c_lo = cr[hb * kTile + fr], c_hi = cr[hb * kTile + fr + 8];
+                acc[f][0] *= c_lo; acc[f][1] *= c_lo; acc[f][2] *= c_hi; acc[f][3] *= c_hi;
+                const bf16* pa = Ph + (size_t)(hb * kTile + fr) * PP + fc;
+                const bf16* pb = Pl + (size_t)(hb * kTile + fr) * PP + fc;
+                const bf16* vb = Vt + (size_t)(((h0 + hb) / per - c_first) * dv + nt * 8 + fr) * VP + fc;
+#pragma unroll
+                for (int k0 = 0; k0 < TK; k0 += 16) {
+                    const uint32_t b0 = ld32(vb + k0), b1 = ld32(vb + k0 + 8);
+                    mma_bf16(acc[f], ld32(pa + k0), ld32(pa + 8 * PP + k0), ld32(pa + k0 + 8), ld32(pa + 8 * PP + k0 + 8), b0, b1);
+                    mma_bf16(acc[f], ld32(pb + k0), ld32(pb + 8 * PP + k0), ld32(pb + k0 + 8), ld32(pb + 8 * PP + k0 + 8), b0, b1);
+                }
+            }
+        }
+    }
+    cluster_sync_all();                         // no block leaves while another may still read its raw scores
+#pragma unroll
+    for (int f = 0; f < kClFrags; f++) {
+        const int t = warp + f * (kClThreads / 32);
+        if (t < n_tiles) {
+            const int hb = t / ntv, nt = t - hb * ntv;
+            const int col = (h0 + hb) * dv + nt * 8 + fc;
+            const float d_lo = dn[hb * kTile + fr], d_hi = dn[hb * kTile + fr + 8];
+            if (fr < nq) {
+                const float inv = d_lo > 0.f ? 1.f / d_lo : 0.f;
+                *reinterpret_cast<__nv_bfloat162*>(out + (int64_t)(row0 + fr) * H * dv + col) =
+                    __floats2bfloat162_rn(acc[f][0] * inv, acc[f][1] * inv);
+            }
+            if (fr + 8 < nq) {
+                const float inv = d_hi > 0.f ? 1.f / d_hi : 0.f;
+                *reinterpret_cast<__nv_bfloat162*>(out + (int64_t)(row0 + fr + 8) * H * dv + col) =
+                    __floats2bfloat162_rn(acc[f][2] * inv, acc[f][3] * inv);
+            }
+        }
+    }
+}
+
+// The blocks of heads of the cluster form for these sizes; NB 0: the form does not take them.
+inline ClShape cl_shape(int H, int G, int dk, int dv) {
+    ClShape s = {H, G, dk, dv, 0, 0, 0};
+    if (dk % 16 || dv % 16) return s;
+    const int per = H / G;
+    for (int nb = 8; nb >= 2; nb--) {
+        if (H % nb) continue;
+        const int hb = H / nb;
+        if (hb * (dv / 8) > (kClThreads / 32) * kClFrags) continue;
+        s.HB = hb;
+        s.NB = nb;
+        s.KV = hb % per == 0 ? hb / per : (per % hb == 0 ? 1 : (hb + per - 1) / per + 1);
+        if (cl_layout(s).total <= 110 * 1024) return s;
+    }
+    s.NB = 0;
+    return s;
+}
+
 // The block of heads and the key tile of the tensor-core form for these sizes; HB 0: the form does not take them.
 inline MmaShape mma_shape(int H, int G, int dk, int dv) {
     MmaShape s = {H, G, dk, dv, 0, 0};
@@ -713,5 +1015,58 @@ extern "C" int kllm_attention_mixed_mma(void* out, const void* q, int64_t q_stri
     kllm_launch((attention_mixed_mma_kernel), dim3(n_tiles, groups), dim3(kMmaThreads), smem, (cudaStream_t)stream, (bf16*)out,
                 (const bf16*)q, q_stride, (const bf16*)kcache, (const bf16*)vcache, mix, sinks, q_start, start_pos, block_table,
                 max_blocks, n_requests, sh, page_size, window, scale);
+    KLLM_LAUNCH_STATUS();
+}
+
+// Whether the cluster form takes these sizes (bfloat16; head sizes in steps of 16; the heads in 2 to 8 equal blocks).
+extern "C" int kllm_attention_mixed_cluster_fits(int n_heads, int n_kv, int dk, int dv) {
+    if (n_heads <= 0 || n_kv <= 0 || n_heads % n_kv || dk <= 0 || dv <= 0) return 0;
+    return cl_shape(n_heads, n_kv, dk, dv).NB > 0 ? 1 : 0;
+}
+
+// The cluster form for bfloat16 portions: operands as in kllm_attention_mixed_mma.  Returns -3 when the device cannot
+// place a cluster of these CTAs, for the caller to take another form.
+extern "C" int kllm_attention_mixed_cluster(void* out, const void* q, int64_t q_stride, const void* kcache, const void* vcache,
+                                            const float* mix, const float* sinks, const int* q_start, const int* start_pos,
+                                            const int* block_table, int max_blocks, int n_requests, int n_tiles, int n_heads,
+                                            int n_kv, int dk, int dv, int page_size, int window, float scale, void* stream) {
+    if (n_requests <= 0 || n_tiles <= 0) return 0;
+    if (n_heads <= 0 || n_kv <= 0 || n_heads % n_kv || page_size <= 0)
+        KLLM_FAIL("mixed attention: %d heads on %d kv heads", n_heads, n_kv);
+    const ClShape sh = cl_shape(n_heads, n_kv, dk, dv);
+    if (sh.NB <= 0) KLLM_FAIL("mixed attention (cluster): head sizes %d, %d of %d heads are not taken", dk, dv, n_heads);
+    if (((uintptr_t)q & 15) || (q_stride % 8) || ((uintptr_t)kcache & 15) || ((uintptr_t)vcache & 15) || ((uintptr_t)out & 3))
+        KLLM_FAIL("mixed attention (cluster): rows must be 16-byte aligned");
+    const size_t smem = cl_layout(sh).total;
+    static bool raised = false;
+    if (!raised) {
+        cudaError_t e = cudaFuncSetAttribute(attention_mixed_cluster_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 110 * 1024);
+        if (e != cudaSuccess) KLLM_FAIL("mixed attention (cluster): %s", cudaGetErrorString(e));
+        raised = true;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(n_tiles, sh.NB);
+    cfg.blockDim = dim3(kClThreads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = (cudaStream_t)stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 1;
+    attr[0].val.clusterDim.y = sh.NB;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    static int placeable[9] = {-1, -1, -1, -1, -1, -1, -1, -1, -1};
+    if (placeable[sh.NB] < 0) {
+        int clusters = 0;
+        cudaError_t e = cudaOccupancyMaxActiveClusters(&clusters, attention_mixed_cluster_kernel, &cfg);
+        placeable[sh.NB] = (e == cudaSuccess && clusters > 0) ? 1 : 0;
+        if (e != cudaSuccess) cudaGetLastError();
+    }
+    if (!placeable[sh.NB]) return -3;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, attention_mixed_cluster_kernel, (bf16*)out, (const bf16*)q, q_stride,
+                                       (const bf16*)kcache, (const bf16*)vcache, mix, sinks, q_start, start_pos, block_table,
+                                       max_blocks, n_requests, sh, page_size, window, scale);
+    if (e != cudaSuccess) KLLM_FAIL("mixed attention (cluster): %s", cudaGetErrorString(e));
     KLLM_LAUNCH_STATUS();
 }

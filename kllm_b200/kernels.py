@@ -1468,7 +1468,8 @@ def lightning_gate_norm(o: torch.Tensor, g: torch.Tensor, gain: torch.Tensor, ep
 # ---- attention with scores mixed across the heads (csrc/attention_mixed.cu) ---------------
 
 _mixed_tile_rows = {}
-MIXED_MMA = os.environ.get("KLLM_B200_MIXED_MMA", "1") != "0"     # bfloat16 portions on the tensor-core form
+MIXED_MMA = os.environ.get("KLLM_B200_MIXED_MMA", "1") != "0"     # bfloat16 portions on the tensor-core forms
+MIXED_CLUSTER = os.environ.get("KLLM_B200_MIXED_CLUSTER", "1") != "0"   # ... of which the cluster form goes first
 
 
 def attention_mixed(out: torch.Tensor, q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, mix: torch.Tensor,
@@ -1480,7 +1481,9 @@ def attention_mixed(out: torch.Tensor, q: torch.Tensor, kcache: torch.Tensor, vc
     denominator of head h.  Scores, mixing, weights and sums are float32 in both dtypes.  Two forms: on the CUDA
     cores, single tokens as tiles of one row and portions as tiles of up to eight rows of one request (float32, and
     every decoding step); on the tensor cores (mma.sync, bfloat16 steps that hold a portion, head sizes in steps of
-    16), tiles of 16 rows by a block of heads, the weights entering the second product as two bfloat16 terms."""
+    16), tiles of 16 rows by a block of heads, the weights entering the second product as two bfloat16 terms: either
+    the blocks of heads of a tile form a thread-block cluster and read each other's raw scores from distributed
+    shared memory (heads in 2 to 8 equal blocks), or every block computes all heads' raw scores itself."""
     _cuda(out, q, kcache, vcache, mix, block_table, sinks)
     _i32(block_table, "block_table"); _i32(ctx.q_start, "q_start"); _i32(ctx.start_pos, "start_pos")
     _slopes_arg(sinks, n_heads, "sinks")
@@ -1496,15 +1499,21 @@ def attention_mixed(out: torch.Tensor, q: torch.Tensor, kcache: torch.Tensor, vc
         raise KernelError("attention_mixed: the mixing matrix must be contiguous float32 [heads, heads]")
     lib = load_library("attention_mixed")
     key = (n_heads, n_kv, head_dim, v_head_dim)
-    if (MIXED_MMA and q.dtype == torch.bfloat16 and not ctx.all_single and q.data_ptr() % 16 == 0 and q.stride(0) % 8 == 0
-            and lib.kllm_attention_mixed_mma_fits(*key)):
+    if (MIXED_MMA and q.dtype == torch.bfloat16 and not ctx.all_single and q.data_ptr() % 16 == 0 and q.stride(0) % 8 == 0):
         tiles = ctx.n_tokens // 16 + ctx.n_requests
-        rc = lib.kllm_attention_mixed_mma(_p(out), _p(q), ctypes.c_int64(q.stride(0)), _p(kcache), _p(vcache), _p(mix),
-                                          _p(sinks), _p(ctx.q_start), _p(ctx.start_pos), _p(block_table),
-                                          block_table.shape[1], ctx.n_requests, int(tiles), n_heads, n_kv, head_dim,
-                                          v_head_dim, page_size, int(window or 0), ctypes.c_float(scale), _stream())
-        _check(lib, "attention_mixed", rc)
-        return
+        args = (_p(out), _p(q), ctypes.c_int64(q.stride(0)), _p(kcache), _p(vcache), _p(mix), _p(sinks), _p(ctx.q_start),
+                _p(ctx.start_pos), _p(block_table), block_table.shape[1], ctx.n_requests, int(tiles), n_heads, n_kv, head_dim,
+                v_head_dim, page_size, int(window or 0), ctypes.c_float(scale), _stream())
+        # first the form in which the blocks of heads of a tile share their raw scores across a cluster of CTAs
+        if MIXED_CLUSTER and lib.kllm_attention_mixed_cluster_fits(*key):
+            rc = lib.kllm_attention_mixed_cluster(*args)
+            if rc != -3:
+                _check(lib, "attention_mixed", rc)
+                return
+        if lib.kllm_attention_mixed_mma_fits(*key):
+            rc = lib.kllm_attention_mixed_mma(*args)
+            _check(lib, "attention_mixed", rc)
+            return
     if key not in _mixed_tile_rows:
         _mixed_tile_rows[key] = int(lib.kllm_attention_mixed_tile_rows(*key))
     rows = _mixed_tile_rows[key]

@@ -433,10 +433,12 @@ def test_mixed_attention_window_edges_far_keys_and_page_borders(dtype, H, G, dk,
     assert np.abs(out.float().cpu().numpy() - plain).max() <= tol * np.abs(plain).max(), "no sink"
 
 
-@pytest.mark.parametrize("H,G,dk,dv", [(8, 2, 64, 64), (32, 8, 128, 128), (6, 3, 16, 48), (20, 1, 16, 32)])
+@pytest.mark.parametrize("H,G,dk,dv", [(8, 2, 64, 64), (32, 8, 128, 128), (6, 3, 16, 48), (20, 1, 16, 32), (12, 4, 32, 16),
+                                       (40, 2, 16, 16), (7, 7, 16, 16), (13, 1, 32, 32)])
 def test_mixed_attention_forms_agree(H, G, dk, dv):
-    """bfloat16 portions: the tensor-core form against the CUDA-core form on the same operands (both keep scores,
-    mixing and weights in float32, so they differ by the order of sums and the weights' second bfloat16 term)."""
+    """bfloat16 portions: the two tensor-core forms (one with a cluster of CTAs that share their raw scores) against
+    the CUDA-core form on the same operands (all keep scores, mixing and weights in float32, so they differ by the
+    order of sums and the weights' second bfloat16 term)."""
     import torch
     from kllm_b200 import kernels
     from kllm_b200.csrc.build import load_library
@@ -451,18 +453,25 @@ def test_mixed_attention_forms_agree(H, G, dk, dv):
     table = torch.arange(pages, dtype=torch.int32, device="cuda").view(1, pages).repeat(3, 1).contiguous()
     ctx = _ctx([1, 150, 37], [199, 13, 0])
     rows = torch.tensor([199] + list(range(13, 163)) + list(range(37)), device="cuda")
-    outs = []
+    outs = {}
+    lib = load_library("attention_mixed")
+    forms = {"cuda cores": (False, False), "tensor cores": (True, False)}
+    if lib.kllm_attention_mixed_cluster_fits(H, G, dk, dv):
+        forms["cluster"] = (True, True)
     try:
-        for form in (True, False):
-            kernels.MIXED_MMA = form
+        for name, (mma, cluster) in forms.items():
+            kernels.MIXED_MMA, kernels.MIXED_CLUSTER = mma, cluster
             out = torch.empty((len(rows), H * dv), dtype=torch.bfloat16, device="cuda")
             kernels.attention_mixed(out, q[rows], kc, vc, mix, ctx, table, H, G, dk, dv, window, dk ** -0.5,
                                     sinks=torch.zeros(H, device="cuda"))
-            outs.append(out.float())
+            outs[name] = out.float()
     finally:
-        kernels.MIXED_MMA = True
-    assert float((outs[0] - outs[1]).abs().max()) <= 2e-2 * float(outs[1].abs().max())
-    assert float((outs[0] - outs[1]).abs().mean()) <= 2e-3 * float(outs[1].abs().max())
+        kernels.MIXED_MMA = kernels.MIXED_CLUSTER = True
+    torch.cuda.synchronize()
+    want = outs.pop("cuda cores")
+    for name, got in outs.items():
+        assert float((got - want).abs().max()) <= 2e-2 * float(want.abs().max()), name
+        assert float((got - want).abs().mean()) <= 2e-3 * float(want.abs().max()), name
 
 
 def test_shared_latent_reads_the_other_layers_rows(tmp_path):
