@@ -299,29 +299,272 @@ attention_mixed_kernel(T* __restrict__ out, float* __restrict__ part_o, float* _
 }
 
 // Joins the key ranges of single tokens: out[t][h][:] = sum_s e^(m_s - M) acc_s / sum_s e^(m_s - M) l_s, in range order.
+// grid (tokens, heads); a thread per value channel.
 template <typename T>
-__global__ void __launch_bounds__(kThreads)
+__global__ void __launch_bounds__(128)
 attention_mixed_merge_kernel(T* __restrict__ out, const float* __restrict__ part_o, const float* __restrict__ part_ml,
                              int splits, int H, int dv) {
     griddep_wait();
     griddep_launch();
-    const int t = blockIdx.x;
-    for (int i = threadIdx.x; i < H * dv; i += kThreads) {
-        const int h = i / dv;
-        const float* pm = part_ml + (size_t)t * splits * H * 2 + 2 * h;
-        float M = -INFINITY;
-        for (int s = 0; s < splits; s++) M = fmaxf(M, pm[(size_t)s * H * 2]);
-        float num = 0.f, den = 0.f;
+    const int t = blockIdx.x, h = blockIdx.y;
+    const float* pm = part_ml + (size_t)t * splits * H * 2 + 2 * h;
+    float M = -INFINITY;
+    for (int s = 0; s < splits; s++) M = fmaxf(M, pm[(size_t)s * H * 2]);
+    float den = 0.f;
+    for (int s = 0; s < splits; s++) {
+        const float m = pm[(size_t)s * H * 2];
+        den = fmaf((m == -INFINITY) ? 0.f : expf(m - M), pm[(size_t)s * H * 2 + 1], den);
+    }
+    const float inv = den > 0.f ? 1.f / den : 0.f;
+    for (int e = threadIdx.x; e < dv; e += blockDim.x) {
+        float num = 0.f;
         for (int s = 0; s < splits; s++) {
             const float m = pm[(size_t)s * H * 2];
             const float w = (m == -INFINITY) ? 0.f : expf(m - M);
-            num = fmaf(w, part_o[((size_t)t * splits + s) * H * dv + i], num);
-            den = fmaf(w, pm[(size_t)s * H * 2 + 1], den);
+            num = fmaf(w, part_o[((size_t)t * splits + s) * H * dv + (size_t)h * dv + e], num);
         }
-        out[(size_t)t * H * dv + i] = from_f32<T>(den > 0.f ? num / den : 0.f);
+        out[(size_t)t * H * dv + (size_t)h * dv + e] = from_f32<T>(num * inv);
     }
 }
 
+// ---- single tokens in bfloat16 ---------------------------------------------------------------------------------
+// A decoding step reads every key and value of its window once and has one row a token: what counts is that the
+// tiles' loads overlap and that little is done per element loaded.  This form keeps the K and V tiles in shared
+// memory as they are stored (bfloat16, copied 16 bytes at a time, both on their way before either is used) and widens
+// them where they are used; a CTA takes one token and one range of its keys, as the general form does.
+struct DecShape {
+    int H, G, dk, dv, TK;
+};
+
+struct DecLayout {
+    size_t q, mix, k, v, raw, p, stats, acc, where, total;
+};
+
+__host__ __device__ inline DecLayout dec_layout(const DecShape& s) {
+    DecLayout L;
+    size_t o = 0;
+    L.where = o;  o += (size_t)s.TK * 8;
+    L.q = o;      o += (size_t)s.H * s.dk * 4;
+    L.mix = o;    o += (size_t)((s.H + 3) / 4) * s.H * 4 * 4;           // [blocks of four heads][H][4]
+    L.k = o;      o += (size_t)s.TK * (s.G * s.dk + 8) * 2;
+    L.v = o;      o += (size_t)s.TK * (s.G * s.dv + 8) * 2;
+    L.raw = o;    o += (size_t)s.H * (s.TK + 1) * 4;
+    L.p = o;      o += (size_t)s.H * (s.TK + 4) * 4;
+    L.stats = o;  o += 3 * (size_t)s.H * 4;
+    o = (o + 15) / 16 * 16;
+    L.acc = o;    o += (size_t)s.H * s.dv * 4;
+    L.total = (o + 15) / 16 * 16;
+    return L;
+}
+
+__device__ __forceinline__ void widen8(const uint4& v, float (&f)[8]) {
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+    for (int u = 0; u < 4; u++) {
+        const float2 x = __bfloat1622float2(h[u]);
+        f[2 * u] = x.x;
+        f[2 * u + 1] = x.y;
+    }
+}
+
+// grid (tokens, ranges).  part_o / part_ml as in attention_mixed_kernel (used when there are several ranges).
+__global__ void __launch_bounds__(kThreads)
+attention_mixed_decode_kernel(bf16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml,
+                              const bf16* __restrict__ q, int64_t q_stride, const bf16* __restrict__ kcache,
+                              const bf16* __restrict__ vcache, const float* __restrict__ mix, const float* __restrict__ sinks,
+                              const int* __restrict__ start_pos, const int* __restrict__ block_table, int max_blocks,
+                              DecShape sh, int page_size, int window, float scale) {
+    extern __shared__ __align__(16) unsigned char smraw[];
+    const int H = sh.H, G = sh.G, dk = sh.dk, dv = sh.dv, TK = sh.TK;
+    const int per = H / G;
+    const DecLayout L = dec_layout(sh);
+    const int KP = G * dk + 8, VP = G * dv + 8, RP = TK + 1, PP = TK + 4;
+    long long* where = reinterpret_cast<long long*>(smraw + L.where);
+    float* qs = reinterpret_cast<float*>(smraw + L.q);          // [H * dk], scaled
+    float* ms = reinterpret_cast<float*>(smraw + L.mix);        // [blocks of four heads][H][4]
+    bf16* Ks = reinterpret_cast<bf16*>(smraw + L.k);            // [TK][KP]
+    bf16* Vs = reinterpret_cast<bf16*>(smraw + L.v);            // [TK][VP]
+    float* raw = reinterpret_cast<float*>(smraw + L.raw);       // [H][RP]
+    float* pr = reinterpret_cast<float*>(smraw + L.p);          // [H][PP]: mixed scores, then weights
+    float* mx = reinterpret_cast<float*>(smraw + L.stats);
+    float* dn = mx + H;
+    float* cr = dn + H;
+    float* acc = reinterpret_cast<float*>(smraw + L.acc);       // [H * dv]
+    const int tid = threadIdx.x;
+    const int hb4 = (H + 3) / 4;
+    for (int i = tid; i < hb4 * H * 4; i += kThreads) {
+        const int u = i & 3, g = (i >> 2) % H, h = (i >> 2) / H * 4 + u;
+        ms[i] = h < H ? mix[(size_t)h * H + g] : 0.f;
+    }
+    griddep_wait();
+    griddep_launch();
+    const int t = blockIdx.x;                                   // token t is request t
+    const int pq = start_pos[t];
+    int hi = pq, lo = window > 0 ? max(0, pq - window + 1) : 0;
+    const int splits = gridDim.y, split = blockIdx.y;
+    if (splits > 1) {
+        const int chunk = (((hi - lo + 1) + splits - 1) / splits + TK - 1) / TK * TK;
+        lo += split * chunk;
+        hi = min(hi, lo + chunk - 1);
+    }
+    const int* table = block_table + (int64_t)t * max_blocks;
+    for (int i = tid; i < H * dk; i += kThreads) qs[i] = __bfloat162float(q[(int64_t)t * q_stride + i]) * scale;
+    for (int h = tid; h < H; h += kThreads) {
+        mx[h] = (sinks && split == 0) ? sinks[h] : -INFINITY;
+        dn[h] = (sinks && split == 0) ? 1.f : 0.f;
+    }
+    for (int i = tid; i < H * dv; i += kThreads) acc[i] = 0.f;
+    const int k8 = G * dk / 8, v8 = G * dv / 8, dk8 = dk / 8, dv8 = dv / 8;
+
+    for (int j0 = lo; j0 <= hi; j0 += TK) {
+        const int nk = min(TK, hi - j0 + 1);
+        __syncthreads();
+        locate_keys(where, table, j0, nk, TK, G, page_size);
+        __syncthreads();
+        // keys and values of the tile, both on their way before either is used
+#pragma unroll 4
+        for (int i = tid; i < nk * k8; i += kThreads) {
+            const int jj = i / k8, c = i - jj * k8, g = c / dk8, d = (c - g * dk8) * 8;
+            const long long at = where[jj];
+            uint4 v = make_uint4(0, 0, 0, 0);
+            if (at >= 0) v = *reinterpret_cast<const uint4*>(kcache + (at + (long long)g * page_size) * dk + d);
+            *reinterpret_cast<uint4*>(Ks + (size_t)jj * KP + g * dk + d) = v;
+        }
+#pragma unroll 4
+        for (int i = tid; i < nk * v8; i += kThreads) {
+            const int jj = i / v8, c = i - jj * v8, g = c / dv8, d = (c - g * dv8) * 8;
+            const long long at = where[jj];
+            uint4 v = make_uint4(0, 0, 0, 0);
+            if (at >= 0) v = *reinterpret_cast<const uint4*>(vcache + (at + (long long)g * page_size) * dv + d);
+            *reinterpret_cast<uint4*>(Vs + (size_t)jj * VP + g * dv + d) = v;
+        }
+        __syncthreads();
+        // raw scores: a thread takes one key of one kv head and up to four of that kv head's query heads at a time
+        const int ub = (per + 3) / 4;
+        for (int it = tid; it < G * ub * TK; it += kThreads) {
+            const int jj = it % TK, rest = it / TK, u0 = (rest % ub) * 4, g = rest / ub;
+            if (jj >= nk) continue;
+            const int nu = min(4, per - u0);
+            const bf16* kr = Ks + (size_t)jj * KP + g * dk;
+            const float* q0 = qs + (size_t)(g * per + u0) * dk;
+            const float* q1 = q0 + (nu > 1 ? dk : 0);
+            const float* q2 = q0 + (nu > 2 ? 2 * dk : 0);
+            const float* q3 = q0 + (nu > 3 ? 3 * dk : 0);
+            float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+            for (int d = 0; d < dk; d += 8) {
+                float kf[8];
+                widen8(*reinterpret_cast<const uint4*>(kr + d), kf);
+#pragma unroll
+                for (int e = 0; e < 8; e += 4) {
+                    const float4 x0 = *reinterpret_cast<const float4*>(q0 + d + e), x1 = *reinterpret_cast<const float4*>(q1 + d + e);
+                    const float4 x2 = *reinterpret_cast<const float4*>(q2 + d + e), x3 = *reinterpret_cast<const float4*>(q3 + d + e);
+                    a0 = fmaf(x0.x, kf[e], a0); a0 = fmaf(x0.y, kf[e + 1], a0); a0 = fmaf(x0.z, kf[e + 2], a0); a0 = fmaf(x0.w, kf[e + 3], a0);
+                    a1 = fmaf(x1.x, kf[e], a1); a1 = fmaf(x1.y, kf[e + 1], a1); a1 = fmaf(x1.z, kf[e + 2], a1); a1 = fmaf(x1.w, kf[e + 3], a1);
+                    a2 = fmaf(x2.x, kf[e], a2); a2 = fmaf(x2.y, kf[e + 1], a2); a2 = fmaf(x2.z, kf[e + 2], a2); a2 = fmaf(x2.w, kf[e + 3], a2);
+                    a3 = fmaf(x3.x, kf[e], a3); a3 = fmaf(x3.y, kf[e + 1], a3); a3 = fmaf(x3.z, kf[e + 2], a3); a3 = fmaf(x3.w, kf[e + 3], a3);
+                }
+            }
+            float* rg = raw + (size_t)(g * per + u0) * RP + jj;
+            rg[0] = a0;
+            if (nu > 1) rg[RP] = a1;
+            if (nu > 2) rg[2 * RP] = a2;
+            if (nu > 3) rg[3 * RP] = a3;
+        }
+        __syncthreads();
+        // mixing and mask: a thread takes one key for four heads
+        for (int it = tid; it < hb4 * TK; it += kThreads) {
+            const int jj = it % TK, b4 = it / TK, b0 = b4 * 4;
+            const int pos = j0 + jj;
+            const bool visible = jj < nk && pos <= pq && (window <= 0 || pq - pos < window);
+            float a0 = -INFINITY, a1 = -INFINITY, a2 = -INFINITY, a3 = -INFINITY;
+            if (visible) {
+                a0 = a1 = a2 = a3 = 0.f;
+                const float4* mw = reinterpret_cast<const float4*>(ms) + (size_t)b4 * H;
+#pragma unroll 4
+                for (int g = 0; g < H; g++) {
+                    const float x = raw[(size_t)g * RP + jj];
+                    const float4 m = mw[g];
+                    a0 = fmaf(m.x, x, a0);
+                    a1 = fmaf(m.y, x, a1);
+                    a2 = fmaf(m.z, x, a2);
+                    a3 = fmaf(m.w, x, a3);
+                }
+            }
+            pr[(size_t)b0 * PP + jj] = a0;
+            if (b0 + 1 < H) pr[(size_t)(b0 + 1) * PP + jj] = a1;
+            if (b0 + 2 < H) pr[(size_t)(b0 + 2) * PP + jj] = a2;
+            if (b0 + 3 < H) pr[(size_t)(b0 + 3) * PP + jj] = a3;
+        }
+        __syncthreads();
+        // one warp per head: maximum, weights, denominator (TK <= 32: a lane per key)
+        {
+            const int lane = tid & 31, warp = tid >> 5;
+            for (int h = warp; h < H; h += kThreads / 32) {
+                float* row = pr + (size_t)h * PP;
+                const float sc = lane < TK ? row[lane] : -INFINITY;
+                const float m_old = mx[h];
+                const float m_new = fmaxf(m_old, warp_max(sc));
+                const float w = (sc == -INFINITY) ? 0.f : expf(sc - m_new);
+                const float c = (m_old == -INFINITY) ? 0.f : expf(m_old - m_new);
+                const float sum = warp_sum(w);
+                if (lane < TK) row[lane] = w;
+                if (lane == 0) {
+                    mx[h] = m_new;
+                    dn[h] = dn[h] * c + sum;
+                    cr[h] = c;
+                }
+            }
+        }
+        __syncthreads();
+        // output: a thread takes eight value channels of one head
+        for (int it = tid; it < H * dv8; it += kThreads) {
+            const int h = it / dv8, e = (it - h * dv8) * 8;
+            const bf16* vr = Vs + (size_t)(h / per) * dv + e;
+            const float* pw = pr + (size_t)h * PP;
+            float a[8];
+#pragma unroll
+            for (int u = 0; u < 8; u++) a[u] = 0.f;
+            for (int jj = 0; jj < nk; jj++) {
+                float vf[8];
+                widen8(*reinterpret_cast<const uint4*>(vr + (size_t)jj * VP), vf);
+                const float w = pw[jj];
+#pragma unroll
+                for (int u = 0; u < 8; u++) a[u] = fmaf(w, vf[u], a[u]);
+            }
+            const float c = cr[h];
+            float* o = acc + (size_t)h * dv + e;
+#pragma unroll
+            for (int u = 0; u < 8; u++) o[u] = o[u] * c + a[u];
+        }
+    }
+    __syncthreads();
+    if (splits > 1) {
+        float* po = part_o + ((size_t)t * splits + split) * H * dv;
+        for (int i = tid; i < H * dv; i += kThreads) po[i] = acc[i];
+        float* pm = part_ml + ((size_t)t * splits + split) * H * 2;
+        for (int h = tid; h < H; h += kThreads) {
+            pm[2 * h] = mx[h];
+            pm[2 * h + 1] = dn[h];
+        }
+        return;
+    }
+    for (int i = tid; i < H * dv; i += kThreads) {
+        const float d = dn[i / dv];
+        out[(int64_t)t * H * dv + i] = __float2bfloat16_rn(d > 0.f ? acc[i] / d : 0.f);
+    }
+}
+
+// The key tile of the single-token form for these sizes; 0: the form does not take them.
+inline DecShape dec_shape(int H, int G, int dk, int dv) {
+    DecShape s = {H, G, dk, dv, 0};
+    if (dk % 8 || dv % 8) return s;
+    for (int tk = 32; tk >= 8; tk /= 2) {
+        s.TK = tk;
+        if (dec_layout(s).total <= 200 * 1024) return s;
+    }
+    s.TK = 0;
+    return s;
+}
 
 // ---- the tensor-core form (bfloat16 portions) ---------------------------------------------------------
 // The same sums with the two products on the tensor cores (mma.sync m16n8k16, bfloat16 operands, float32
@@ -927,6 +1170,28 @@ extern "C" int kllm_attention_mixed(void* out, const void* q, int64_t q_stride, 
     if (tile_rows < 1 || tile_rows > kMaxTQ) KLLM_FAIL("mixed attention: tiles of %d rows (1 to %d)", tile_rows, kMaxTQ);
     if (splits < 1 || (splits > 1 && (tile_rows != 1 || n_tiles != n_requests || !part_o || !part_ml)))
         KLLM_FAIL("mixed attention: %d key ranges need single tokens and room for the ranges' results", splits);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == KLLM_BF16 && tile_rows == 1 && n_tiles == n_requests && dec_shape(n_heads, n_kv, dk, dv).TK > 0 &&
+        !(((uintptr_t)kcache | (uintptr_t)vcache) & 15)) {
+        // every request one token: the form that keeps the tiles in bfloat16 (token t is request t)
+        const DecShape ds = dec_shape(n_heads, n_kv, dk, dv);
+        const size_t need = dec_layout(ds).total;
+        static bool raised_dec = false;
+        if (need > 48 * 1024 && !raised_dec) {
+            cudaFuncSetAttribute(attention_mixed_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+            raised_dec = true;
+        }
+        kllm_launch((attention_mixed_decode_kernel), dim3(n_tiles, splits), dim3(kThreads), need, s, (bf16*)out, part_o, part_ml,
+                    (const bf16*)q, q_stride, (const bf16*)kcache, (const bf16*)vcache, mix, sinks, start_pos, block_table,
+                    max_blocks, ds, page_size, window, scale);
+        if (splits > 1) {
+            cudaError_t e = cudaGetLastError();
+            if (e != cudaSuccess) KLLM_FAIL("mixed attention: %s", cudaGetErrorString(e));
+            kllm_launch((attention_mixed_merge_kernel<bf16>), dim3(n_tiles, n_heads), dim3(128), 0, s, (bf16*)out, part_o, part_ml,
+                        splits, n_heads, dv);
+        }
+        KLLM_LAUNCH_STATUS();
+    }
     const size_t budget = 200 * 1024;
     Shape sh = {n_heads, n_kv, dk, dv, tile_rows, 32};
     while (sh.TK > 4 && smem_floats(sh) * sizeof(float) > budget) sh.TK /= 2;
@@ -934,7 +1199,6 @@ extern "C" int kllm_attention_mixed(void* out, const void* q, int64_t q_stride, 
     if (sh.TQ != tile_rows) KLLM_FAIL("mixed attention: tiles of %d rows do not fit shared memory (%d would)", tile_rows, sh.TQ);
     const size_t smem = smem_floats(sh) * sizeof(float);
     if (smem > budget) KLLM_FAIL("mixed attention: %d heads of sizes %d, %d do not fit shared memory", n_heads, dk, dv);
-    cudaStream_t s = (cudaStream_t)stream;
     static bool raised[2] = {false, false};
     if (dtype == KLLM_F32) {
         if (smem > 48 * 1024 && !raised[0]) {
@@ -959,10 +1223,10 @@ extern "C" int kllm_attention_mixed(void* out, const void* q, int64_t q_stride, 
         cudaError_t e = cudaGetLastError();
         if (e != cudaSuccess) KLLM_FAIL("mixed attention: %s", cudaGetErrorString(e));
         if (dtype == KLLM_F32)
-            kllm_launch((attention_mixed_merge_kernel<float>), dim3(n_tiles), dim3(kThreads), 0, s, (float*)out, part_o, part_ml,
+            kllm_launch((attention_mixed_merge_kernel<float>), dim3(n_tiles, n_heads), dim3(128), 0, s, (float*)out, part_o, part_ml,
                         splits, n_heads, dv);
         else
-            kllm_launch((attention_mixed_merge_kernel<bf16>), dim3(n_tiles), dim3(kThreads), 0, s, (bf16*)out, part_o, part_ml,
+            kllm_launch((attention_mixed_merge_kernel<bf16>), dim3(n_tiles, n_heads), dim3(128), 0, s, (bf16*)out, part_o, part_ml,
                         splits, n_heads, dv);
     }
     KLLM_LAUNCH_STATUS();
@@ -970,6 +1234,9 @@ extern "C" int kllm_attention_mixed(void* out, const void* q, int64_t q_stride, 
 
 // The keys of a tile on the CUDA-core form for these sizes and rows (what the cutting into ranges counts in).
 extern "C" int kllm_attention_mixed_tile_keys(int n_heads, int n_kv, int dk, int dv, int tile_rows) {
+    // (the bfloat16 single-token form's tile where it takes the sizes: the float32 form's tiles are no larger, and
+    // every form cuts the ranges in whole tiles of its own)
+    if (tile_rows == 1 && dec_shape(n_heads, n_kv, dk, dv).TK > 0) return dec_shape(n_heads, n_kv, dk, dv).TK;
     Shape sh = {n_heads, n_kv, dk, dv, tile_rows, 32};
     while (sh.TK > 4 && smem_floats(sh) * sizeof(float) > 200 * 1024) sh.TK /= 2;
     return sh.TK;
