@@ -86,7 +86,23 @@ CFG_C = {
         _layer("attention", _attn(20, 1, 16, 32, 0.2, 33, (500.0, 16)), None),
     ],
 }
-CFGS = {"A": (CFG_A, 51), "B": (CFG_B, 52), "C": (CFG_C, 53)}
+# D: sizes in steps of 16 as a small served model has them, other than C's: heads in blocks that straddle kv heads on
+# the cluster form (12 heads on 4 kv heads), values wider than keys, a window that is no multiple of a page or a
+# tile, two readers of one latent, recurrent layers of many small heads, a token side input of a vector width.
+CFG_D = {
+    "architecture": "Senulix", "vocab": 160, "width": 256, "norm": {"eps": 1e-6}, "token_side": {"dim": 32},
+    "logit_softcap": 25.0,
+    "layers": [
+        _layer("latent_attention", _latent(4, 48, 32, 32, 96, 0.11, 20000.0), 320),
+        _layer("attention", _attn(12, 4, 32, 48, 0.18, 77, (20000.0, 16)), 320),
+        _layer("lightning", _light(8, 16, 32, [0.7, 0.8, 0.9, 0.95, 0.97, 0.98, 0.99, 0.995]), None),
+        _layer("latent_attention", _latent(8, 16, 32, 16, 96, 0.14, 20000.0, kv_from=0), 192),
+        _layer("attention", _attn(4, 4, 48, 16, 0.14, 130, (20000.0, 48)), 192),
+        _layer("latent_attention", _latent(2, 64, 32, 64, 96, 0.1, 20000.0, kv_from=0), None),
+        _layer("lightning", _light(2, 64, 64, [0.9, 0.99]), 256),
+    ],
+}
+CFGS = {"A": (CFG_A, 51), "B": (CFG_B, 52), "C": (CFG_C, 53), "D": (CFG_D, 54)}
 
 
 def make_model(tmp_path, name, qk_boost=2.0):
@@ -99,7 +115,7 @@ def make_model(tmp_path, name, qk_boost=2.0):
 # ---- whole models --------------------------------------------------------------------------
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 def test_whole_prompt_and_every_way_of_cutting(tmp_path, name, dtype):
     cfg, w, d = make_model(tmp_path, name, 2.0 if dtype == "float32" else 1.0)
     rng = np.random.default_rng(5)
@@ -218,12 +234,13 @@ def test_greedy_generation_through_the_scheduler(tmp_path):
             ids.append(out[k])
 
 
-def test_replay_program(tmp_path):
+@pytest.mark.parametrize("name", ["A", "D"])
+def test_replay_program(tmp_path, name):
     """bin/trace_run on a model of this design: whole, decode, portions and mixed batches of up
     to four live requests in a pool as small as the trace allows."""
     from test_gpu_replay import build_trace
     from trace_tools import run_trace
-    cfg, w, d = make_model(tmp_path, "A", 1.0)
+    cfg, w, d = make_model(tmp_path, name, 1.0)
     rng = np.random.default_rng(4)
     seqs = [rng.integers(0, cfg["vocab"], size=n).tolist() for n in (5, 33, 64, 100, 18)]
     want = [P.forward(w, cfg, s) for s in seqs]
